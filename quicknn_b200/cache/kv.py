@@ -46,6 +46,7 @@ class LineView:
     slot_len: torch.Tensor          # [slots] int32 (device): length after the running step
     state: Optional[torch.Tensor]   # [slots, *shape] or None
     writes: bool = True
+    has_values: bool = True         # False: ``v`` is ``k`` (a line that keeps one row per position)
 
 
 class CacheGroup:
@@ -62,7 +63,7 @@ class CacheGroup:
         self.pool = PagePool(n_pages)
         shape = (len(lines), n_pages, need.n_kv_heads, PAGE, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device) if need.values else self.k
         self.table_host = np.zeros((max_slots, self.pages_per_seq), dtype=np.int32)
         self.table_dev = torch.zeros((max_slots, self.pages_per_seq), dtype=torch.int32, device=device)
         self.held: List[List[int]] = [[] for _ in range(max_slots)]
@@ -72,7 +73,7 @@ class CacheGroup:
         return min(_round_up(length, PAGE) // PAGE, self.pages_per_seq)
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (2 if self.need.values else 1) * self.k.numel() * self.k.element_size()
 
 
 class KVCache:
@@ -232,7 +233,7 @@ class KVCache:
             return LineView(None, None, None, 0, PAGE, self.lengths_dev, st, writes)
         gi, li = self._line_group[line]
         g = self.groups[gi]
-        return LineView(g.k[li], g.v[li], g.table_dev, g.ring, PAGE, self.lengths_dev, st, writes)
+        return LineView(g.k[li], g.v[li], g.table_dev, g.ring, PAGE, self.lengths_dev, st, writes, g.need.values)
 
     def bytes(self) -> int:
         return sum(g.bytes() for g in self.groups) + sum(t.numel() * t.element_size() for t in self.state.values())
@@ -241,7 +242,7 @@ class KVCache:
         """Bytes of keys and values that one decode step of these sequences has to read."""
         total = 0
         for g in self.groups:
-            per_tok = 2 * g.need.n_kv_heads * g.need.head_dim * g.k.element_size() * len(g.lines)
+            per_tok = (2 if g.need.values else 1) * g.need.n_kv_heads * g.need.head_dim * g.k.element_size() * len(g.lines)
             for s in slots:
                 n = int(self.lengths_host[s])
                 if g.need.window is not None:

@@ -15,7 +15,7 @@ from __future__ import annotations
 import dataclasses
 import json
 import os
-from typing import Any, Callable, Dict, List, Optional, Tuple, Type
+from typing import Any, Callable, Dict, List, Mapping, Optional, Tuple, Type
 
 
 class ConfigError(ValueError):
@@ -161,6 +161,9 @@ class Architecture:
     # config -> quicknn_b200.parts.spec.ModelSpec
     build_spec: Callable[[ModelConfig], Any]
     aliases: Tuple[str, ...] = ()
+    # (raw config, tensor name -> shape) -> raw config: fills in sizes that the architecture's config.json
+    # leaves to the checkpoint's tensor shapes; None when the config says everything
+    sizes_from_shapes: Optional[Callable[[Dict[str, Any], Mapping[str, Tuple[int, ...]]], Dict[str, Any]]] = None
 
 
 _REGISTRY: Dict[str, Architecture] = {}
@@ -188,7 +191,7 @@ def registered_architectures() -> List[str]:
 
 
 def find_architecture(raw: Dict[str, Any]) -> Architecture:
-    """Pick the architecture from ``architectures[0]`` and then ``model_type``."""
+    """Pick the architecture from ``architectures[0]``, then ``model_type``, then ``architecture``."""
     tried: List[str] = []
     archs = raw.get("architectures")
     if isinstance(archs, (list, tuple)):
@@ -197,11 +200,12 @@ def find_architecture(raw: Dict[str, Any]) -> Architecture:
                 tried.append(a)
                 if a in _REGISTRY:
                     return _REGISTRY[a]
-    mt = raw.get("model_type")
-    if isinstance(mt, str):
-        tried.append(mt)
-        if mt in _REGISTRY:
-            return _REGISTRY[mt]
+    for key in ("model_type", "architecture"):       # a single name under either key
+        mt = raw.get(key)
+        if isinstance(mt, str):
+            tried.append(mt)
+            if mt in _REGISTRY:
+                return _REGISTRY[mt]
     raise ConfigError(
         [f"no registered architecture for {tried or 'a config without architectures/model_type'}; "
          f"registered: {registered_architectures()}"])
@@ -216,4 +220,15 @@ def load_config(model_dir_or_file: str) -> Tuple[Architecture, ModelConfig]:
     if not isinstance(raw, dict):
         raise ConfigError(["config.json is not a JSON object"], where=path)
     arch = find_architecture(raw)
+    if arch.sizes_from_shapes is not None and os.path.isdir(model_dir_or_file):
+        from ..weights.safetensors_io import TensorDirectory      # headers only; no tensor is read
+        try:
+            d = TensorDirectory.open(model_dir_or_file)
+        except (OSError, ValueError):
+            d = None
+        if d is not None:
+            try:
+                raw = arch.sizes_from_shapes(raw, {n: tuple(d.shape_dtype(n)[0]) for n in d.names()})
+            finally:
+                d.close()
     return arch, arch.config_cls.from_dict(raw)

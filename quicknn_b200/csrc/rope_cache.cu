@@ -69,7 +69,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int nq, int nkv, int hd, 
             dst[d + 1] = x[d + 1];
         }
     }
-    if (wr) {
+    if (wr && v_pool != nullptr) {                 // a line that keeps keys only has no value pool
         for (int w = threadIdx.x; w < nkv * hd; w += blockDim.x) {
             const int h = w / hd, d = w % hd;
             v_pool[cache_base + (size_t)h * head_stride + d] = v[w];
@@ -116,7 +116,7 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, int nq, int nkv, int 
     const int rc = rh / VEC;                       // rotating items per head
     const int pc = (hd - rot) / VEC;               // pass-through items per kv head
     const int vc = hd / VEC;                       // value items per kv head
-    const int n_rot = (nq + nkv) * rc, n_pass = wr ? nkv * pc : 0, n_val = wr ? nkv * vc : 0;
+    const int n_rot = (nq + nkv) * rc, n_pass = wr ? nkv * pc : 0, n_val = (wr && v_pool != nullptr) ? nkv * vc : 0;
     for (int w = threadIdx.x; w < n_rot + n_pass + n_val; w += blockDim.x) {
         if (w < n_rot) {
             const int h = w / rc, j = (w % rc) * VEC;

@@ -49,6 +49,10 @@ class Model:
             blk.load(local, self.dtype, self.device)
             self.blocks.append(blk)
         self.embedding = tensors[spec.embedding.tensor].contiguous()
+        self.embedding_norm = None
+        if spec.embedding.norm is not None:
+            self.embedding_norm = NORMS.get(spec.embedding.norm.kind)(spec.embedding.norm)
+            self.embedding_norm.load({"weight": tensors[spec.embedding.norm_tensor]}, self.dtype, self.device)
         self.final_norm = NORMS.get(spec.head.norm.kind)(spec.head.norm)
         self.final_norm.load({"weight": tensors[spec.head.norm_tensor]}, self.dtype, self.device)
         self.head = self.embedding if spec.head.tied else tensors[spec.head.tensor].contiguous()
@@ -63,14 +67,14 @@ class Model:
         arch, cfg = load_config(model_dir)
         spec = arch.build_spec(cfg)
         want = {n: s for n, (s, _) in expected_tensors(spec).items()}
-        tensors = load_named_tensors(model_dir, want, as_dtype(dtype), device)
+        tensors = load_named_tensors(model_dir, want, as_dtype(dtype), device, optional=spec.optional_tensors)
         return cls(arch, cfg, tensors, dtype, device)
 
     @classmethod
     def from_tensors(cls, arch: Architecture, cfg: ModelConfig, tensors: Mapping[str, torch.Tensor],
                      dtype="bfloat16", device="cuda:0") -> "Model":
         spec = arch.build_spec(cfg)
-        check_state_dict({n: s for n, (s, _) in expected_tensors(spec).items()}, tensors)
+        check_state_dict({n: s for n, (s, _) in expected_tensors(spec).items()}, tensors, optional=spec.optional_tensors)
         placed = {n: place(t, as_dtype(dtype), device) for n, t in tensors.items()}
         return cls(arch, cfg, placed, dtype, device)
 
@@ -117,6 +121,8 @@ class Model:
         n = self.embedding.numel() * self.embedding.element_size()
         if self.head is not self.embedding:
             n += self.head.numel() * self.head.element_size()
+        if self.embedding_norm is not None:
+            n += self.embedding_norm.weight_bytes()
         return n + self.final_norm.weight_bytes() + sum(b.weight_bytes() for b in self.blocks)
 
     def step_weight_bytes(self) -> int:
@@ -134,7 +140,11 @@ class Model:
         spec = self.spec
         sched = spec.schedule
         first = self.blocks[sched[0].layer].first_norm() if sched else None
-        if hasattr(first, "of_embedding"):
+        if self.embedding_norm is not None:
+            # the normed rows are the stream itself (float32), not a sublayer's input
+            x = self.embedding_norm(ops.embed(step.tokens, self.embedding, spec.embedding.scale), torch.float32)
+            normed = None
+        elif hasattr(first, "of_embedding"):
             # the first layer's first norm in the embedding's kernel; the layer is handed its input normed
             x, normed = first.of_embedding(step.tokens, self.embedding, spec.embedding.scale, step.act_dtype)
         else:

@@ -203,6 +203,8 @@ def rope_cache_write(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, 
     _req(tok_slot, "tok_slot", torch.int32, 1)
     if write_cache:
         for n, t in (("k_pool", k_pool), ("v_pool", v_pool)):
+            if t is None and n == "v_pool":            # a line that keeps keys only
+                continue
             _req(t, n, qkv.dtype, 4)
             if tuple(t.shape[1:]) != (n_kv, page_size, head_dim):
                 raise ValueError(f"{n} has shape {tuple(t.shape)}, expected [pages, {n_kv}, {page_size}, {head_dim}]")
@@ -225,8 +227,8 @@ def cache_append(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_
     f = _no_freq.get(qkv.device)
     if f is None:
         f = _no_freq[qkv.device] = torch.zeros(0, dtype=torch.float32, device=qkv.device)
-    rope_cache_write(qkv, n_heads, n_kv, head_dim, 0, f, tok_pos, tok_slot, line.k, line.v, line.page_table,
-                     line.page_size, line.ring, line.slot_len, True)
+    rope_cache_write(qkv, n_heads, n_kv, head_dim, 0, f, tok_pos, tok_slot, line.k, line.v if line.has_values else None,
+                     line.page_table, line.page_size, line.ring, line.slot_len, True)
 
 
 FUSE_ROPE = os.environ.get("QNN_FUSE_ROPE", "1") != "0"
@@ -785,3 +787,207 @@ def mark_seen(tokens: torch.Tensor, rows: torch.Tensor, seen: torch.Tensor):
     L = _lib.load()
     _lib.check(L.qnn_mark_seen(_p(tokens), _p(rows), _p(seen), seen.shape[1], tokens.numel(), _stream()),
                "mark_seen")
+
+
+# ---- the residual stream with a multiplier, norms over pieces of rows -----------------------------------
+
+def add_scaled_rmsnorm(resid: torch.Tensor, y: torch.Tensor, scale: float, w_next: Optional[torch.Tensor] = None,
+                       eps_next: float = 0.0, unit_next: bool = False, out_dtype: Optional[torch.dtype] = None):
+    """resid += scale * y (float32 stream, in place); returns rmsnorm(resid, w_next) when ``w_next`` is given."""
+    _req(resid, "resid", torch.float32, 2)
+    _req(y, "y", None, 2)
+    T, H = resid.shape
+    if tuple(y.shape) != (T, H) or (w_next is not None and w_next.numel() != H):
+        raise ValueError("add_scaled_rmsnorm: shapes do not agree")
+    out = None
+    if w_next is not None:
+        _req(w_next, "w_next", None, 1)
+        out = torch.empty((T, H), dtype=out_dtype, device=resid.device)
+    _lib.check(_lib.load().qnn_add_scaled_rmsnorm(
+        _p(resid), _p(y), dt_code(y), float(scale), _p(w_next), dt_code(w_next) if w_next is not None else 0,
+        float(eps_next), int(unit_next), _p(out), dt_code(out) if out is not None else 0, T, H, _stream()),
+        "add_scaled_rmsnorm")
+    return out
+
+
+def _col_ptr(t: torch.Tensor, col: int):
+    return ctypes.c_void_p(t.data_ptr() + col * t.element_size())
+
+
+def rmsnorm_cols(x: torch.Tensor, col0: int, n: int, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                 out_col0: int = 0, out2_col0: Optional[int] = None) -> torch.Tensor:
+    """RMS norm (plain weight) of the columns ``col0 .. col0 + n`` of every row of ``x``, written to the columns
+    ``out_col0 ..`` of ``out`` and, if given, once more to ``out2_col0 ..``: a piece of a stacked product's
+    rows normed into a packed buffer, float32 math."""
+    _req(x, "x", None, 2)
+    _req(out, "out", None, 2)
+    _req(weight, "weight", None, 1)
+    T = x.shape[0]
+    ends = [out_col0 + n] + ([out2_col0 + n] if out2_col0 is not None else [])
+    if out.shape[0] != T or weight.numel() != n or col0 + n > x.shape[1] or max(ends) > out.shape[1]:
+        raise ValueError("rmsnorm_cols: shapes do not agree")
+    _lib.check(_lib.load().qnn_rmsnorm_strided(
+        _col_ptr(x, col0), dt_code(x), x.shape[1], _p(weight), dt_code(weight), float(eps), _col_ptr(out, out_col0),
+        dt_code(out), out.shape[1], _col_ptr(out, out2_col0) if out2_col0 is not None else None, out.shape[1], T, n,
+        _stream()), "rmsnorm_strided")
+    return out
+
+
+def copy_cols(src: torch.Tensor, dst: torch.Tensor, dst_col0: int) -> torch.Tensor:
+    """dst[:, dst_col0 : dst_col0 + src.shape[1]] = src, rows of the same element type."""
+    _req(src, "src", None, 2)
+    _req(dst, "dst", src.dtype, 2)
+    T, n = src.shape
+    if dst.shape[0] != T or dst_col0 + n > dst.shape[1]:
+        raise ValueError("copy_cols: shapes do not agree")
+    _lib.check(_lib.load().qnn_copy_rows(_p(src), dt_code(src), n, _col_ptr(dst, dst_col0), dst.shape[1], T, n, _stream()),
+               "copy_rows")
+    return dst
+
+
+def scale_heads(x: torch.Tensor, gate_logits: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """x[t, h, :] *= sigmoid(gate_logits[t, h]) in place; the gate is float32."""
+    _req(x, "x", None, 2)
+    _req(gate_logits, "gate_logits", torch.float32, 2)
+    T, HD = x.shape
+    if HD % n_heads or tuple(gate_logits.shape) != (T, n_heads):
+        raise ValueError("scale_heads: shapes do not agree")
+    _lib.check(_lib.load().qnn_scale_heads(_p(x), dt_code(x), _p(gate_logits), T, n_heads, HD // n_heads, _stream()),
+               "scale_heads")
+    return x
+
+
+def small_linear_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x w^T with float32 sums and a float32 result, whatever the element types: for the few outputs that feed
+    float32 math (a gate per head, decay logits).  A plain kernel; the order of a sum depends on the inner size only."""
+    _req(x, "x", None, 2)
+    _req(w, "w", None, 2)
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise ValueError(f"small_linear_f32: x is [*, {K}] but w is [*, {w.shape[1]}]")
+    out = torch.empty((T, N), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().qnn_small_linear_f32(_p(x), dt_code(x), _p(w), dt_code(w), _p(out), T, N, K, _stream()),
+               "small_linear_f32")
+    return out
+
+
+# ---- gated linear attention -------------------------------------------------------------------------------
+
+def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, bias: torch.Tensor, tau: float,
+             q_scale: float, seq_row0: Optional[torch.Tensor], seq_len: Optional[torch.Tensor], slots: torch.Tensor,
+             state: torch.Tensor, n_seqs: int, n_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """The recurrence S = diag(a) S + k v^T, o = S^T (q q_scale) with a = sigmoid(z + bias)^(1/tau), over the rows
+    of every sequence in order, from the state of the sequence's slot and back into it.  ``proj`` holds q and k
+    ([*, heads*dim]) and v ([*, heads*vdim]) from the given columns on; returns o, float32 [rows, heads*vdim]."""
+    _req(proj, "proj", None, 2)
+    _req(z, "z", torch.float32, 2)
+    _req(bias, "bias", None, 1)
+    _req(slots, "slots", torch.int32, 1)
+    _req(state, "state", torch.float32)
+    T = proj.shape[0]
+    if tuple(z.shape) != (T, n_heads * dim) or bias.numel() != n_heads * dim or slots.numel() < n_seqs:
+        raise ValueError("gla_scan: shapes do not agree")
+    if tuple(state.shape[1:]) != (n_heads, dim, vdim):
+        raise ValueError(f"gla_scan: the state is {tuple(state.shape)}, expected [slots, {n_heads}, {dim}, {vdim}]")
+    if (seq_row0 is None) != (seq_len is None):
+        raise ValueError("gla_scan: first rows and row counts come together")
+    if seq_row0 is None and T < n_seqs:
+        raise ValueError("gla_scan: fewer rows than sequences")
+    out = torch.empty((T, n_heads * vdim), dtype=torch.float32, device=proj.device)
+    _lib.check(_lib.load().qnn_gla_scan(
+        _col_ptr(proj, q_col), _col_ptr(proj, k_col), _col_ptr(proj, v_col), proj.shape[1], dt_code(proj), _p(z),
+        z.shape[1], _p(bias), dt_code(bias), float(tau), float(q_scale), _p(seq_row0), _p(seq_len), _p(slots), _p(state),
+        _p(out), out.shape[1], n_seqs, n_heads, dim, vdim, _stream()), "gla_scan")
+    return out
+
+
+def gla_norm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, proj: torch.Tensor, g_col: int, n_heads: int,
+                  vdim: int) -> torch.Tensor:
+    """Per head: RMS norm of ``o`` over vdim (weight shared by the heads), times silu of the gate columns of
+    ``proj``; returns [rows, heads*vdim] of proj's element type."""
+    _req(o, "o", torch.float32, 2)
+    _req(proj, "proj", None, 2)
+    _req(weight, "weight", None, 1)
+    T = o.shape[0]
+    if o.shape[1] != n_heads * vdim or weight.numel() != vdim or proj.shape[0] != T or g_col + n_heads * vdim > proj.shape[1]:
+        raise ValueError("gla_norm_gate: shapes do not agree")
+    out = torch.empty((T, n_heads * vdim), dtype=proj.dtype, device=o.device)
+    _lib.check(_lib.load().qnn_gla_norm_gate(_p(o), o.shape[1], _p(weight), dt_code(weight), float(eps),
+                                             _col_ptr(proj, g_col), proj.shape[1], _p(out), out.shape[1], dt_code(proj),
+                                             T, n_heads, vdim, _stream()), "gla_norm_gate")
+    return out
+
+
+# ---- routed experts -----------------------------------------------------------------------------------------
+
+MOE_SCORES = {"sigmoid": 0, "softmax": 1}
+GATED_CLAMPED = 2            # the gated activation g' * sigmoid(alpha g') * (u' + 1) of clamped g', u'
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False):
+    """(expert ids int32 [rows*top], scores float32 [rows*top]): the ``top`` best experts of every row by
+    score(x w_router^T), logits and scores in float32, ties to the lower index."""
+    _req(x, "x", None, 2)
+    _req(w_router, "w_router", None, 2)
+    T, W = x.shape
+    E = w_router.shape[0]
+    if w_router.shape[1] != W:
+        raise ValueError("moe_route: the router's inner size differs from the rows'")
+    sel_e = torch.empty(T * top, dtype=torch.int32, device=x.device)
+    sel_w = torch.empty(T * top, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().qnn_moe_route(_p(x), dt_code(x), _p(w_router), dt_code(w_router), T, W, E, int(top),
+                                         MOE_SCORES[score], int(renormalize), _p(sel_e), _p(sel_w), _stream()),
+               "moe_route")
+    return sel_e, sel_w
+
+
+def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: int, w_gate_up: torch.Tensor,
+                w_down: torch.Tensor, activation: int, limit: float, alpha: float, weight_on_input: bool,
+                shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """sum over a row's chosen experts of down_e(act(gate_e(x'), up_e(x'))) (+ ``shared``), float32 [rows, width].
+    The score multiplies the expert's input (x' = score * x) or its output.  w_gate_up: [experts, 2*ff, width]
+    (gate rows, then up rows); w_down: [experts, width, ff].  Everything stays on the device."""
+    _req(x, "x", None, 2)
+    _req(w_gate_up, "w_gate_up", x.dtype, 3)
+    _req(w_down, "w_down", x.dtype, 3)
+    T, W = x.shape
+    E, ff2, _ = w_gate_up.shape
+    ff = ff2 // 2
+    if tuple(w_gate_up.shape) != (E, 2 * ff, W) or tuple(w_down.shape) != (E, W, ff) or sel_e.numel() != T * top:
+        raise ValueError("moe_experts: shapes do not agree")
+    L = _lib.load()
+    n = T * top
+    max_tiles = int(L.qnn_moe_max_tiles(n, E))
+    meta = torch.empty(E + 1 + n + 2 * max_tiles + 1, dtype=torch.int32, device=x.device)
+    offsets, perm = meta[:E + 1], meta[E + 1:E + 1 + n]
+    tiles, n_tiles = meta[E + 1 + n:E + 1 + n + 2 * max_tiles], meta[E + 1 + n + 2 * max_tiles:]
+    _lib.check(L.qnn_moe_plan(_p(sel_e), n, E, _p(offsets), _p(perm), _p(tiles), _p(n_tiles), _stream()), "moe_plan")
+    hidden = torch.empty((n, ff), dtype=x.dtype, device=x.device)
+    _lib.check(L.qnn_moe_gate_up(_p(x), dt_code(x), W, _p(w_gate_up), ff, _p(offsets), _p(perm), _p(sel_w), _p(tiles),
+                                 _p(n_tiles), max_tiles, top, int(weight_on_input), int(activation), float(limit),
+                                 float(alpha), _p(hidden), _stream()), "moe_gate_up")
+    ys = torch.empty((n, W), dtype=torch.float32, device=x.device)
+    _lib.check(L.qnn_moe_down(_p(hidden), dt_code(x), ff, _p(w_down), W, _p(offsets), _p(perm), _p(sel_w), _p(tiles),
+                              _p(n_tiles), max_tiles, int(not weight_on_input), _p(ys), _stream()), "moe_down")
+    if top == 1 and shared is None:
+        return ys
+    if shared is not None:
+        _req(shared, "shared", None, 2)
+        if tuple(shared.shape) != (T, W):
+            raise ValueError("moe_experts: the shared expert's output has another shape")
+    out = torch.empty((T, W), dtype=torch.float32, device=x.device)
+    _lib.check(L.qnn_moe_combine(_p(ys), top, _p(shared), dt_code(shared) if shared is not None else 0, _p(out), T, W,
+                                 _stream()), "moe_combine")
+    return out
+
+
+def gated_act_clamped(gu: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """[rows, 2*I] (gate | up) -> [rows, I]: g = min(gate, limit), u = clamp(up, -limit, limit),
+    g * sigmoid(alpha * g) * (u + 1)."""
+    _req(gu, "gate_up", None, 2)
+    T, I2 = gu.shape
+    out = torch.empty((T, I2 // 2), dtype=gu.dtype, device=gu.device)
+    _lib.check(_lib.load().qnn_gated_act_clamped(_p(gu), _p(out), dt_code(gu), T, I2 // 2, float(limit), float(alpha),
+                                                 _stream()), "gated_act_clamped")
+    return out

@@ -4,7 +4,7 @@ from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Block, Cache
 from .spec import (EmbeddingSpec, HeadSpec, LayerSpec, ModelSpec, PartSpec, ScheduleEntry,
                    default_schedule)
 from .layout import expected_tensors
-from . import attention, block, feedforward, norm, position  # noqa: F401  (register the built-in kinds)
+from . import attention, block, feedforward, gla, latent_attention, moe, norm, position  # noqa: F401  (register the built-in kinds)
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "Block", "CacheNeed", "FeedForward",
            "HeadShape", "Mixer", "Norm", "Part", "PartRegistry", "Positions", "StateNeed", "EmbeddingSpec", "HeadSpec",

@@ -135,6 +135,14 @@ class AttentionMixer(Mixer):
         if qkv is None:
             qkv = project(x, self.w_qkv)
             self.position.place(qkv, h, step, line, append=not extend)
+        return project(self.attend(qkv, step, line), self.w_o)
+
+    def attend(self, qkv: torch.Tensor, step, line) -> torch.Tensor:
+        """Attention of the packed q|k|v rows of a step, by the step's mode.  In prefill and decode the keys and
+        values are in the cache line already; a step that continues sequences by several rows appends them
+        here, after the attention.  Returns [rows, heads * head_dim]."""
+        h = self.heads
+        extend = step.mode == "extend"
         if extend and line.writes:
             # cached keys from before this step, this step's own rows from there on; the append comes last,
             # so that the first rows still find the ring cells that the last rows overwrite
@@ -163,4 +171,4 @@ class AttentionMixer(Mixer):
             a = ops.attn_decode(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v, line.page_table,
                                 line.page_size, line.ring, step.slots, line.slot_len, self.scale, self.softcap,
                                 self.window, splits, part[:n * self.head_dim], part[n * self.head_dim:n * (self.head_dim + 2)])
-        return project(a, self.w_o)
+        return a

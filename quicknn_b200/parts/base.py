@@ -72,14 +72,16 @@ BLOCKS = PartRegistry("block")
 @dataclasses.dataclass(frozen=True)
 class CacheNeed:
     """Keys and values that grow with the sequence.  ``window`` = None keeps every
-    position; an integer keeps the last ``window`` positions (a ring)."""
+    position; an integer keeps the last ``window`` positions (a ring).  With ``values`` False only
+    one row per position is kept (the view's ``v`` is its ``k``)."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True          # False: the line keeps keys only (a latent that serves as key and value)
 
     def group_key(self) -> Tuple:
-        return (self.n_kv_heads, self.head_dim, self.window)
+        return (self.n_kv_heads, self.head_dim, self.window, self.values)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -109,7 +111,8 @@ class Part:
     """Common base: parameters by local name."""
 
     PARAM_ROLE_MATRIX = "matrix"
-    PARAM_ROLE_NORM = "norm"
+    PARAM_ROLE_NORM = "norm"          # drawn around 0: weights applied as 1 + w, biases
+    PARAM_ROLE_SCALE = "scale"        # drawn around 1: weights that multiply as they are
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

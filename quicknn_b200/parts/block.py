@@ -3,7 +3,8 @@
 ``sandwich`` (Gemma 2, src/models/QuickNN.Models.Gemma2.pas:166-189): a norm before
 and after each sublayer, the post-norm applied to the sublayer's output before it
 is added:  x += post(mixer(pre(x)));  x += post(ff(pre(x))).
-``prenorm``: x += mixer(pre(x));  x += ff(pre(x)).
+``prenorm``: x += m mixer(pre(x));  x += m ff(pre(x)), with a constant m (``residual_mult``, 1 unless given) and a
+feed-forward that a layer may lack.
 
 The residual stream is float32 in both precisions.  When the norms are RMSNorm the
 post-norm, the add and the next pre-norm run as one kernel; that also holds across the
@@ -29,20 +30,29 @@ class _LayerParts(Block):
         super().__init__(layer.block)
         self.layer = layer
         self.mixer = MIXERS.get(layer.mixer.kind)(layer.mixer)
-        self.ff = FEED_FORWARDS.get(layer.feed_forward.kind)(layer.feed_forward)
-        missing = [n for n in self.NORM_NAMES if n not in layer.norms]
+        self.ff = None if layer.feed_forward is None else FEED_FORWARDS.get(layer.feed_forward.kind)(layer.feed_forward)
+        names = self.norm_names(layer)
+        missing = [n for n in names if n not in layer.norms]
         if missing:
             raise ValueError(f"block '{layer.block.kind}' needs the norms {missing}")
-        self.norms = {n: NORMS.get(layer.norms[n].kind)(layer.norms[n]) for n in self.NORM_NAMES}
+        self.norms = {n: NORMS.get(layer.norms[n].kind)(layer.norms[n]) for n in names}
+
+    @classmethod
+    def norm_names(cls, layer: LayerSpec) -> Tuple[str, ...]:
+        """The norms that this arrangement has for this layer (a layer without a feed-forward has none around it)."""
+        if layer.feed_forward is None:
+            return tuple(n for n in cls.NORM_NAMES if not n.endswith("_ff"))
+        return cls.NORM_NAMES
 
     @classmethod
     def layer_param_shapes(cls, layer: LayerSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         out: Dict[str, Tuple[Tuple[int, ...], str]] = {}
         for k, v in MIXERS.get(layer.mixer.kind).param_shapes(layer.mixer).items():
             out["mixer." + k] = v
-        for k, v in FEED_FORWARDS.get(layer.feed_forward.kind).param_shapes(layer.feed_forward).items():
-            out["ff." + k] = v
-        for n in cls.NORM_NAMES:
+        if layer.feed_forward is not None:
+            for k, v in FEED_FORWARDS.get(layer.feed_forward.kind).param_shapes(layer.feed_forward).items():
+                out["ff." + k] = v
+        for n in cls.norm_names(layer):
             for k, v in NORMS.get(layer.norms[n].kind).param_shapes(layer.norms[n]).items():
                 out[f"norms.{n}.{k}"] = v
         return out
@@ -51,18 +61,20 @@ class _LayerParts(Block):
         def sub(prefix):
             return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
         self.mixer.load(sub("mixer."), compute_dtype, device)
-        self.ff.load(sub("ff."), compute_dtype, device)
+        if self.ff is not None:
+            self.ff.load(sub("ff."), compute_dtype, device)
         for n, part in self.norms.items():
             part.load(sub(f"norms.{n}."), compute_dtype, device)
 
     def weight_bytes(self) -> int:
-        return self.mixer.weight_bytes() + self.ff.weight_bytes() + sum(n.weight_bytes() for n in self.norms.values())
+        return (self.mixer.weight_bytes() + (self.ff.weight_bytes() if self.ff is not None else 0)
+                + sum(n.weight_bytes() for n in self.norms.values()))
 
     def scratch_need(self, step) -> int:
-        return max(self.mixer.scratch_need(step), self.ff.scratch_need(step))
+        return max(self.mixer.scratch_need(step), self.ff.scratch_need(step) if self.ff is not None else 0)
 
     def schedule(self, step) -> tuple:
-        return self.mixer.schedule(step) + self.ff.schedule(step)
+        return self.mixer.schedule(step) + (self.ff.schedule(step) if self.ff is not None else ())
 
 
 @BLOCKS.register("sandwich")
@@ -103,11 +115,29 @@ class PreNormBlock(_LayerParts):
     def first_norm(self):
         return self.norms["pre_mixer"]
 
+    def __init__(self, layer: LayerSpec):
+        super().__init__(layer)
+        # what a sublayer gives is multiplied by this constant before it is added (1: the usual pre-norm block)
+        self.mult = float(layer.block.get("residual_mult", 1.0))
+
+    def _add(self, resid: torch.Tensor, y: torch.Tensor, then, act):
+        """resid += mult * y, and then(resid) in the same kernel when ``then`` is an RMSNorm."""
+        if isinstance(then, RMSNorm):
+            return ops.add_scaled_rmsnorm(resid, y, self.mult, then.weight, then.eps, then.unit_offset, act)
+        if self.mult == 1.0:
+            ops.add_(resid, y)
+        else:
+            ops.add_scaled_rmsnorm(resid, y, self.mult)
+        return None if then is None else then(resid, act)
+
     def forward(self, resid: torch.Tensor, step, line, normed=None, next_norm=None):
         act = step.act_dtype
         n = normed if normed is not None else self.norms["pre_mixer"](resid, act)
-        ops.add_(resid, self.mixer.forward(n, step, line))
-        ops.add_(resid, self.ff.forward(self.norms["pre_ff"](resid, act), step))
+        y = self.mixer.forward(n, step, line)
+        if self.ff is not None:
+            n = self._add(resid, y, self.norms["pre_ff"], act)
+            y = self.ff.forward(n, step)
+        n = self._add(resid, y, next_norm, act)
         if next_norm is not None:
-            return resid, next_norm(resid, act)
+            return resid, n
         return resid

@@ -1,0 +1,85 @@
+"""Gated linear attention: a recurrent mixer whose state is a matrix per head.
+
+    q = W_q x * dim^(-1/2),  k = W_k x  (heads x dim),   v = W_v x  (heads x vdim)
+    a = sigmoid(W_a2 (W_a1 x) + b)^(1/tau)               a decay per key channel, float32
+    S_t = diag(a_t) S_{t-1} + k_t v_t^T,   o_t = S_t^T q_t                 S: [dim, vdim] float32 per head
+    y = W_o ( rmsnorm_per_head(o) * silu(W_g x) )
+
+The state lives in the cache's fixed-size state region, one [heads, dim, vdim] float32 block per slot, zeroed
+when the slot is handed out; the mixer needs no keys or values.  A step walks each sequence's rows in order from
+the slot's state and leaves the new state there, so whole prompts, portions and single tokens are one kernel.
+q, k, v and the gate are one stacked product; the decay's logits are formed in float32 from the low-rank
+projection's output, and the decay itself (log-sigmoid, division by tau, exponential) inside the scan.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..kernels import ops
+from .base import MIXERS, CacheNeed, Mixer, StateNeed
+from .linear import project, stack_rows
+from .spec import PartSpec
+
+
+@MIXERS.register("gla")
+class GatedLinearAttention(Mixer):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["n_heads"])
+        self.dim = int(p["dim"])
+        self.vdim = int(p["vdim"])
+        self.decay_rank = int(p["decay_rank"])
+        self.tau = float(p["tau"])
+        self.eps = float(p["eps"])
+        if not self.tau > 0:
+            raise ValueError(f"gla: tau must be positive (got {self.tau})")
+        if self.dim > 256:
+            raise ValueError(f"gla: at most 256 key channels per head (got {self.dim})")
+        self.w_in: Optional[torch.Tensor] = None         # q | k | v | gate rows
+        self.w_a1: Optional[torch.Tensor] = None
+        self.w_a2: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self.norm: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        p = spec.params
+        W, H, d, vd, ra = int(p["hidden_size"]), int(p["n_heads"]), int(p["dim"]), int(p["vdim"]), int(p["decay_rank"])
+        M, N = cls.PARAM_ROLE_MATRIX, cls.PARAM_ROLE_SCALE
+        return {"q": ((H * d, W), M), "k": ((H * d, W), M), "v": ((H * vd, W), M), "gate": ((H * vd, W), M),
+                "o": ((W, H * vd), M), "norm": ((vd,), N), "a1": ((ra, W), M), "a2": ((H * d, ra), M),
+                "a2_bias": ((H * d,), cls.PARAM_ROLE_NORM)}
+
+    def load(self, tensors, compute_dtype, device) -> None:
+        self.w_in = stack_rows([tensors["q"], tensors["k"], tensors["v"], tensors["gate"]])
+        self.w_a1 = tensors["a1"].contiguous()
+        self.w_a2 = tensors["a2"].contiguous()
+        self.bias = tensors["a2_bias"].contiguous()
+        self.norm = tensors["norm"].contiguous()
+        self.w_o = tensors["o"].contiguous()
+
+    def weight_bytes(self) -> int:
+        ws = (self.w_in, self.w_a1, self.w_a2, self.bias, self.norm, self.w_o)
+        return sum(w.numel() * w.element_size() for w in ws)
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return StateNeed((self.n_heads, self.dim, self.vdim), "float32")
+
+    def forward(self, x: torch.Tensor, step, line) -> torch.Tensor:
+        H, d, vd = self.n_heads, self.dim, self.vdim
+        p = project(x, self.w_in)                                         # q | k | v | gate
+        z = ops.small_linear_f32(project(x, self.w_a1), self.w_a2)        # decay logits, float32
+        o = ops.gla_scan(p, 0, H * d, 2 * H * d, z, self.bias, self.tau, float(d) ** -0.5,
+                         None if step.mode == "decode" else step.seq_row0,
+                         None if step.mode == "decode" else step.seq_len,
+                         step.slots, line.state, step.n_seqs, H, d, vd)
+        g = ops.gla_norm_gate(o, self.norm, self.eps, p, 2 * H * d + H * vd, H, vd)
+        return project(g, self.w_o)

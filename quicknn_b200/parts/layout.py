@@ -17,6 +17,9 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         out[name] = (tuple(shape), role)
 
     put(spec.embedding.tensor, (spec.embedding.vocab_size, spec.embedding.hidden_size), Part.PARAM_ROLE_MATRIX)
+    if spec.embedding.norm is not None:
+        for k, (shape, role) in NORMS.get(spec.embedding.norm.kind).param_shapes(spec.embedding.norm).items():
+            put(spec.embedding.norm_tensor if k == "weight" else f"{spec.embedding.norm_tensor}.{k}", shape, role)
     for li, layer in enumerate(spec.layers):
         shapes = BLOCKS.get(layer.block.kind).layer_param_shapes(layer)
         for local, (shape, role) in shapes.items():

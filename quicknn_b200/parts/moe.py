@@ -1,0 +1,116 @@
+"""Feed-forwards with a clamped gated activation, dense and routed.
+
+``clamped_mlp``: down(act(gate(x), up(x))) with  g = min(gate, limit),  u = clamp(up, -limit, limit),
+act = g * sigmoid(alpha * g) * (u + 1)  (alpha 1.702 unless given).
+
+``routed_experts``: ``experts`` such feed-forwards, of which every token uses the ``top`` with the largest router
+scores.  Router logits and scores are float32; scores are sigmoid(logit) (or a softmax over the experts), optionally
+renormalised over the chosen ones; the score multiplies the expert's *input* (``weight_on`` = "input": the
+sum over the chosen experts of expert(score * x)) or its output.  A shared expert of the same form, with sizes and
+limit of its own, may run for every token beside them.  Everything from the router to the sum stays on the
+device (no count is read back), so a decode step with routed layers is captured in a CUDA graph like any other.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..kernels import ops
+from .base import FEED_FORWARDS, FeedForward
+from .linear import project, stack_rows
+from .spec import PartSpec
+
+
+@FEED_FORWARDS.register("clamped_mlp")
+class ClampedMLP(FeedForward):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.limit = float(spec.params["limit"])
+        self.alpha = float(spec.get("alpha", 1.702))
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        H, I = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        M = cls.PARAM_ROLE_MATRIX
+        return {"gate_proj": ((I, H), M), "up_proj": ((I, H), M), "down_proj": ((H, I), M)}
+
+    def load(self, tensors, compute_dtype, device) -> None:
+        self.w_gate_up = stack_rows([tensors["gate_proj"], tensors["up_proj"]])
+        self.w_down = tensors["down_proj"].contiguous()
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))
+
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        h = ops.gated_act_clamped(project(x, self.w_gate_up), self.limit, self.alpha)
+        return project(h, self.w_down)
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.n_experts = int(p["experts"])
+        self.top = int(p["top"])
+        self.inter = int(p["intermediate_size"])
+        self.limit = float(p["limit"])
+        self.alpha = float(p.get("alpha", 1.702))
+        self.score = str(p.get("score", "sigmoid"))
+        self.renormalize = bool(p.get("renormalize", False))
+        self.weight_on_input = str(p.get("weight_on", "input")) == "input"
+        if not (1 <= self.top <= self.n_experts) or self.top > 16:
+            raise ValueError(f"routed experts: top {self.top} of {self.n_experts} experts (at most 16)")
+        if self.score not in ops.MOE_SCORES:
+            raise ValueError(f"routed experts: score {self.score!r} is not one of {sorted(ops.MOE_SCORES)}")
+        shared: Optional[PartSpec] = p.get("shared")
+        self.shared = None if shared is None else FEED_FORWARDS.get(shared.kind)(shared)
+        self.w_router: Optional[torch.Tensor] = None
+        self.w_gate_up: Optional[torch.Tensor] = None      # [experts, 2 * ff, width]
+        self.w_down: Optional[torch.Tensor] = None         # [experts, width, ff]
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        p = spec.params
+        H, I, E = int(p["hidden_size"]), int(p["intermediate_size"]), int(p["experts"])
+        M = cls.PARAM_ROLE_MATRIX
+        out: Dict[str, Tuple[Tuple[int, ...], str]] = {"router": ((E, H), M)}
+        for e in range(E):
+            out[f"experts.{e}.gate_proj"] = ((I, H), M)
+            out[f"experts.{e}.up_proj"] = ((I, H), M)
+            out[f"experts.{e}.down_proj"] = ((H, I), M)
+        shared: Optional[PartSpec] = p.get("shared")
+        if shared is not None:
+            for k, v in FEED_FORWARDS.get(shared.kind).param_shapes(shared).items():
+                out["shared." + k] = v
+        return out
+
+    def load(self, tensors, compute_dtype, device) -> None:
+        E = self.n_experts
+        self.w_router = tensors["router"].contiguous()
+        self.w_gate_up = torch.stack([stack_rows([tensors[f"experts.{e}.gate_proj"], tensors[f"experts.{e}.up_proj"]])
+                                      for e in range(E)]).contiguous()
+        self.w_down = torch.stack([tensors[f"experts.{e}.down_proj"] for e in range(E)]).contiguous()
+        if self.w_gate_up.dtype != self.w_down.dtype:
+            wide = torch.float32
+            self.w_gate_up, self.w_down = self.w_gate_up.to(wide), self.w_down.to(wide)
+        if self.shared is not None:
+            self.shared.load({k[len("shared."):]: v for k, v in tensors.items() if k.startswith("shared.")},
+                             compute_dtype, device)
+
+    def weight_bytes(self) -> int:
+        n = sum(w.numel() * w.element_size() for w in (self.w_router, self.w_gate_up, self.w_down))
+        return n + (self.shared.weight_bytes() if self.shared is not None else 0)
+
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        sel_e, sel_w = ops.moe_route(x, self.w_router, self.top, self.score, self.renormalize)
+        shared = self.shared.forward(x, step) if self.shared is not None else None
+        xe = x if x.dtype == self.w_gate_up.dtype else ops.cast(x, self.w_gate_up.dtype)
+        return ops.moe_experts(xe, sel_e, sel_w, self.top, self.w_gate_up, self.w_down, ops.GATED_CLAMPED, self.limit,
+                               self.alpha, self.weight_on_input, shared)

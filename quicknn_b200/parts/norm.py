@@ -26,7 +26,8 @@ class RMSNorm(Norm):
 
     @classmethod
     def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
-        return {"weight": ((int(spec.params["size"]),), cls.PARAM_ROLE_NORM)}
+        role = cls.PARAM_ROLE_NORM if spec.get("unit_offset", False) else cls.PARAM_ROLE_SCALE
+        return {"weight": ((int(spec.params["size"]),), role)}
 
     def load(self, tensors, compute_dtype, device) -> None:
         self.weight = tensors["weight"].contiguous()

@@ -31,7 +31,7 @@ class LayerSpec:
 
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]      # None: the layer is its mixer alone
     norms: Mapping[str, PartSpec]
     tensors: Mapping[str, str]
 
@@ -53,6 +53,8 @@ class EmbeddingSpec:
     hidden_size: int
     scale: float                      # multiplies the looked-up row (fp32 scalar)
     tensor: str                       # checkpoint name of the table
+    norm: Optional[PartSpec] = None   # a norm that the looked-up rows pass through before they become the stream
+    norm_tensor: str = ""
 
 
 @dataclasses.dataclass(frozen=True)
@@ -79,6 +81,8 @@ class ModelSpec:
     # standard deviations that the random-weights mode uses: matrices, norm weights
     init_std: float = 0.02
     init_norm_std: float = 0.1
+    # checkpoint tensors that may be there and are not used (name -> shape is not checked)
+    optional_tensors: Tuple[str, ...] = ()
 
     def n_cache_lines(self) -> int:
         return 1 + max((e.cache for e in self.schedule), default=-1)

@@ -42,9 +42,10 @@ class WeightError(ValueError):
 
 def check_names_and_shapes(expected: Mapping[str, Tuple[int, ...]],
                            found: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]],
-                           where: str = "") -> None:
+                           where: str = "", optional: Sequence[str] = ()) -> None:
+    """``optional``: names that may be found without being expected (tensors the model does not use)."""
     missing = [n for n in expected if n not in found]
-    unexpected = [n for n in found if n not in expected]
+    unexpected = [n for n in found if n not in expected and n not in set(optional)]
     wrong_shape, wrong_dtype = [], []
     for n, want in expected.items():
         if n in found:
@@ -68,11 +69,11 @@ def place(t: torch.Tensor, compute_dtype: torch.dtype, device) -> torch.Tensor:
 
 
 def load_named_tensors(model_dir: str, expected: Mapping[str, Tuple[int, ...]],
-                       compute_dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
+                       compute_dtype: torch.dtype, device, optional: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
     d = TensorDirectory.open(model_dir)
     try:
         found = {n: d.shape_dtype(n) for n in d.names()}
-        check_names_and_shapes(expected, found, where=model_dir)
+        check_names_and_shapes(expected, found, where=model_dir, optional=optional)
         out: Dict[str, torch.Tensor] = {}
         for n in expected:
             out[n] = place(d.tensor(n), compute_dtype, device)
@@ -82,6 +83,6 @@ def load_named_tensors(model_dir: str, expected: Mapping[str, Tuple[int, ...]],
 
 
 def check_state_dict(expected: Mapping[str, Tuple[int, ...]],
-                     tensors: Mapping[str, torch.Tensor]) -> None:
+                     tensors: Mapping[str, torch.Tensor], optional: Sequence[str] = ()) -> None:
     check_names_and_shapes(expected, {n: (tuple(t.shape), t.dtype) for n, t in tensors.items()},
-                           where="(in memory)")
+                           where="(in memory)", optional=optional)

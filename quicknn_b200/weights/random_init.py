@@ -33,9 +33,9 @@ def random_tensors(arch: Architecture, cfg: ModelConfig, seed: int, dtype: torch
     for name, (shape, role) in expected_tensors(spec).items():
         g = torch.Generator(device=device)
         g.manual_seed(_tensor_seed(seed, name))
-        std = nstd if role == Part.PARAM_ROLE_NORM else spec.init_std
+        std = nstd if role in (Part.PARAM_ROLE_NORM, Part.PARAM_ROLE_SCALE) else spec.init_std
         t = torch.empty(shape, dtype=torch.float32, device=device)
-        t.normal_(0.0, std, generator=g)
+        t.normal_(1.0 if role == Part.PARAM_ROLE_SCALE else 0.0, std, generator=g)
         yield name, t.to(dtype)
 
 
