@@ -50,18 +50,16 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict_
         if (lane == 0) s[e] = d;
     }
     __syncwarp();
+    // Both score functions rise with the logit, so the experts are chosen by their logits (a sigmoid that has
+    // run into 1.0 would tie where the logits still differ) and only the chosen ones' scores are formed.
+    float m = -INFINITY, sum = 1.f;
     if (score_fn == QNN_MOE_SCORE_SOFTMAX) {
-        float m = -INFINITY;
         for (int e = lane; e < E; e += 32) m = fmaxf(m, s[e]);
         m = warp_max(m);
-        float sum = 0.f;
+        sum = 0.f;
         for (int e = lane; e < E; e += 32) sum += expf(s[e] - m);
         sum = warp_sum(sum);
-        for (int e = lane; e < E; e += 32) s[e] = expf(s[e] - m) / sum;
-    } else {
-        for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-s[e]));
     }
-    __syncwarp();
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -76,7 +74,8 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict_
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
-        if (arg == 0x7fffffff) arg = 0;                    // scores that are all NaN: any expert, the logits will show it
+        if (arg == 0x7fffffff) arg = 0;                    // logits that are all NaN: any expert, the model's logits will show it
+        best = score_fn == QNN_MOE_SCORE_SOFTMAX ? expf(best - m) / sum : 1.f / (1.f + expf(-best));
         total += best;
         if (lane == 0) {
             sel_e[(size_t)t * top + k] = arg;
