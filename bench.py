@@ -259,6 +259,90 @@ def timed_tiny(torch):
     return out
 
 
+# ---- another design beside its closest model at equal size (--design) ------------------------------------
+
+def design_sizes(name):
+    """(Fuposun config, Gemma 2 config) with the same width, depth, vocabulary, window and dense feed-forward width.
+    ``2b``: the 2B layer sizes; ``1b``: about half of them.  Layers come in the pattern latent attention + dense,
+    latent attention + experts, linear attention + dense, latent attention + experts."""
+    W, ff, heads, hd, kvh, layers, vocab, window = {
+        "2b": (2304, 9216, 8, 256, 4, 8, 32768, 4096), "1b": (1536, 6144, 8, 128, 4, 8, 32768, 2048)}[name]
+    rank, qr, d = (256, 768, 128) if name == "2b" else (128, 512, 64)
+    H = W // d // 2                                            # latent heads: heads * vdim = width / 2 ... width
+    latent = {"heads": 2 * H // 2, "dim": d, "vdim": d, "q_rank": qr, "kv_rank": rank, "scale": d ** -0.5, "mask": {"size": window}}
+    gla = {"heads": W // (2 * d), "dim": d, "vdim": 2 * d, "tau": 16.0, "decay_rank": 64}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": ff // 4, "limit": 7.0},
+           "shared": {"ff": ff // 4, "limit": 7.0}}
+    pattern = [("latent_attention", latent, dense), ("latent_attention", latent, moe), ("gla", gla, dense),
+               ("latent_attention", latent, moe)]
+    fupo = dict(architecture="Fuposun", vocab=vocab, width=W, residual_mult=0.7, logit_softcap=30.0, norm={"eps": 1e-5},
+                layers=[{"type": t, "mixer": m, "mlp": f} for t, m, f in (pattern * layers)[:layers]])
+    gemma = dict(SIZES, hidden_size=W, intermediate_size=ff, num_attention_heads=heads, num_key_value_heads=kvh,
+                 head_dim=hd, num_hidden_layers=layers, vocab_size=vocab, sliding_window=window,
+                 query_pre_attn_scalar=hd)
+    return fupo, gemma
+
+
+def design_run(args, torch, pk):
+    """Prefill and decode throughput of the other design and of Gemma 2 at equal size, and for both where a step's
+    time goes by kernel wrapper with each wrapper's distance from its roofline."""
+    from quicknn_b200.engine import LLM, OpTimer
+    out = {"design": args.design, "peaks": pk, "decode_batch": args.batch, "decode_context": args.context,
+           "prefill_tokens": PREFILL_TOKENS, "sizes": {}}
+    for size in args.design_sizes.split(","):
+        out["sizes"][size] = {}
+        for which, cfg in zip((args.design, "gemma2"), design_sizes(size)):
+            vocab = cfg.get("vocab", cfg.get("vocab_size"))
+            llm = LLM.random(cfg, SEED, dtype="bfloat16", max_context=args.context, max_batch=args.batch,
+                             max_tokens=args.batch * args.context)
+            eng = llm.engine
+            ids = torch.randint(1, vocab, (PREFILL_TOKENS,)).tolist()
+            times = []
+            for i in range(6):
+                slot = eng.new_sequence()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                eng.step([(slot, ids)], "last")
+                e1.record()
+                torch.cuda.synchronize()
+                eng.release(slot)
+                if i >= 3:
+                    times.append(e0.elapsed_time(e1))
+            pre_ms = statistics.median(times)
+            dec = timed_decode(eng, args.batch, min(args.steps, 128), args.warmup, torch, context=args.context)
+            rec = {"weight_bytes": eng.model.weight_bytes(),
+                   "prefill": {"tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3), "tokens_per_s": round(PREFILL_TOKENS / pre_ms * 1e3, 1)},
+                   "decode": {"tokens_per_s": round(dec["tok_s"], 1), "ms_per_step": round(dec["ms_per_step"], 4),
+                              "hbm_frac": round(dec["bytes_per_step"] / (dec["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 3),
+                              "launches_per_step": dec["launches"] // max(1, min(args.steps, 128))}}
+            # by kernel wrapper: one prompt, then eager decode steps at the context
+            slot = eng.new_sequence()
+            with OpTimer(eng, pk["hbm_gbs"], pk["bf16_tflops"]) as t:
+                eng.step([(slot, ids)], "last")
+            rec["prefill_ops"] = t.rows()
+            eng.release(slot)
+            slots = [eng.new_sequence() for _ in range(args.batch)]
+            fill_synthetic(eng, slots, [args.context - 8] * args.batch, torch)
+            toks = torch.randint(1, vocab, (args.batch,), dtype=torch.int32, device=eng.device)
+            eng.decode(slots, toks, use_graph=False)
+            with OpTimer(eng, pk["hbm_gbs"], pk["bf16_tflops"], context=args.context - 6) as t:
+                for _ in range(4):
+                    eng.decode(slots, toks, use_graph=False)
+            rows = t.rows()
+            for r in rows:
+                r["ms"], r["least_ms"], r["calls"] = round(r["ms"] / 4, 4), round(r["least_ms"] / 4, 4), r["calls"] // 4
+            rec["decode_ops"] = rows
+            out["sizes"][size][which] = rec
+            del llm, eng
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -276,6 +360,9 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-baseline", action="store_true", help="do not time the plain PyTorch / NumPy baselines")
+    ap.add_argument("--design", default=None, choices=["fuposun"],
+                    help="instead of the record: this design beside Gemma 2 at equal size (prefill, decode, kernels)")
+    ap.add_argument("--design-sizes", default="1b,2b", help="with --design: which of 1b, 2b")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -295,6 +382,10 @@ def main():
     from quicknn_b200.sampling import GenerationOptions
 
     pk = peaks()
+    if args.design:
+        if args.context == CONTEXT:
+            args.context = 4096
+        return design_run(args, torch, pk)
     base = dict(SIZES, **OTHER_SIZES.get(args.model, {}))
     if args.layers is None:
         args.layers = base["num_hidden_layers"]

@@ -12,9 +12,11 @@
 //   qnn_gated_act_clamped   the clamped activation for a dense product: g = min(gate, limit),
 //                      u = clamp(up, -limit, limit), g * sigmoid(alpha g) * (u + 1)
 //
-// The two tile kernels are plain FMA kernels for both element types: 16 rows x 128 output columns per block,
-// 32 inner elements at a time through shared memory.  Sums run over the inner size in a fixed order, so a row's
-// result does not depend on which other rows share its tile.
+// The tile kernels: bfloat16 with inner sizes in whole blocks of 32 runs on the tensor cores (mma.sync, 16 or 64 rows
+// x 64 output columns per block, weights read as 16-byte operand pieces straight from global memory); everything
+// else (float32, other inner sizes) on plain FMA kernels, 16 rows x 128 columns per block, 32 inner elements at a
+// time through shared memory.  Sums run over the inner size in a fixed order, so a row's result does not depend on
+// which other rows share its tile.
 #include "common.cuh"
 
 using namespace qnn;
@@ -35,20 +37,36 @@ constexpr int MAX_TOP = 16;
 template <typename TX, typename TW>
 __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict__ wr, int T, int W, int E, int top,
                                  int score_fn, int renorm, int* __restrict__ sel_e, float* __restrict__ sel_w) {
-    extern __shared__ float sc[];                       // [warps][E]
+    extern __shared__ float sc[];                       // [E]
     pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= T) return;
-    float* s = sc + (size_t)warp * E;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    const int t = blockIdx.x;
+    float* s = sc;
     const TX* xr = x + (size_t)t * W;
-    for (int e = 0; e < E; ++e) {
+    // the warps share the experts; a lane's terms and the order of their sum depend on the width only
+    constexpr int VX = Vec16<TX>::N, VW = Vec16<TW>::N, V = VX > VW ? VX : VW;
+    const bool vec = (W % V) == 0 && ((((uintptr_t)x | (uintptr_t)wr) & 15) == 0);
+    for (int e = warp; e < E; e += nwarp) {
         const TW* wrow = wr + (size_t)e * W;
         float d = 0.f;
-        for (int i = lane; i < W; i += 32) d += to_f(xr[i]) * to_f(wrow[i]);
+        if (vec) {
+            for (int i = lane * V; i < W; i += 32 * V) {
+                float xf[V], wf[V];
+#pragma unroll
+                for (int j = 0; j < V; j += VX) { Vec16<TX> v; v.load(xr + i + j); v.unpack(xf + j); }
+#pragma unroll
+                for (int j = 0; j < V; j += VW) { Vec16<TW> v; v.load(wrow + i + j); v.unpack(wf + j); }
+#pragma unroll
+                for (int j = 0; j < V; ++j) d += xf[j] * wf[j];
+            }
+        } else {
+            for (int i = lane; i < W; i += 32) d += to_f(xr[i]) * to_f(wrow[i]);
+        }
         d = warp_sum(d);
         if (lane == 0) s[e] = d;
     }
+    __syncthreads();
+    if (warp != 0) return;
     __syncwarp();
     // Both score functions rise with the logit, so the experts are chosen by their logits (a sigmoid that has
     // run into 1.0 would tie where the logits still differ) and only the chosen ones' scores are formed.
@@ -92,7 +110,7 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict_
 
 // offsets: [E + 1]; perm: [n] sorted place -> entry (row * top + k); tiles: [max_tiles][2] (expert, first sorted
 // place); n_tiles: [1].  Which of an expert's rows comes first varies from run to run; no result depends on it.
-__global__ void moe_plan_kernel(const int* __restrict__ sel_e, int n, int E, int* __restrict__ offsets,
+__global__ void moe_plan_kernel(const int* __restrict__ sel_e, int n, int E, int tile_rows, int* __restrict__ offsets,
                                 int* __restrict__ perm, int* __restrict__ tiles, int* __restrict__ n_tiles) {
     extern __shared__ int cnt[];                        // [E] counts, then [E] running places
     int* at = cnt + E;
@@ -106,7 +124,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ sel_e, int n, int E, int
         for (int e = 0; e < E; ++e) {
             offsets[e] = o;
             at[e] = o;
-            for (int r = 0; r < cnt[e]; r += TILE_ROWS) {
+            for (int r = 0; r < cnt[e]; r += tile_rows) {
                 tiles[2 * nt] = e;
                 tiles[2 * nt + 1] = o + r;
                 ++nt;
@@ -231,6 +249,169 @@ moe_down_kernel(const T* __restrict__ hidden, int ff, const T* __restrict__ w_do
         }
 }
 
+// ---- the same tiles on the tensor cores (bfloat16) -----------------------------------------------------------------
+// A block owns MT x 16 rows of one expert and 64 output columns (4 warps x 2 column tiles of 8).  The rows' activations
+// pass through shared memory 256 inner elements at a time; the weights never do: a lane reads 16 bytes of a weight
+// row straight into the B operand.  That is possible because a sum over the inner index may run in any order: within
+// a block of 32 inner elements lane (g, tg) takes elements 8 tg .. 8 tg + 7 of weight row g, which are the B pairs
+// of two m16n8k16 steps, and the A operand takes the same elements of the activation rows (one 16-byte load from
+// shared memory per row half).  Sums are float32; a row's result does not depend on the other rows of its tile.
+
+constexpr int MMA_WARPS = 4, MMA_NW = 2, MMA_COLS = MMA_WARPS * MMA_NW * 8, MMA_KC = 256, MMA_PITCH = MMA_KC + 32;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// acc[m][t][j] += rows x weights over K (a multiple of 32) for NM matrices; `fill(k0, kn)` puts the rows' elements
+// k0 .. k0 + kn - 1 into xs ([MT*16][MMA_PITCH] bfloat16, zero rows beyond the tile's).
+template <int MT, int NM, typename Fill>
+__device__ __forceinline__ void mma_tile_product(const bf16* const (&w)[NM], int col0, int n_cols, int K, bf16* xs,
+                                                 float (&acc)[NM][MT][MMA_NW][4], Fill fill) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
+    const bf16* wrow[NM][MMA_NW];
+#pragma unroll
+    for (int m = 0; m < NM; ++m)
+#pragma unroll
+        for (int t = 0; t < MMA_NW; ++t) {
+            const int c = min((warp * MMA_NW + t) * 8 + g, n_cols - 1);          // columns beyond the matrix: any row, unused
+            wrow[m][t] = w[m] + (size_t)(col0 + c) * K + 8 * tg;
+        }
+    for (int k0 = 0; k0 < K; k0 += MMA_KC) {
+        const int kn = min(MMA_KC, K - k0);
+        __syncthreads();
+        fill(k0, kn);
+        __syncthreads();
+        uint4 bnext[NM][MMA_NW];
+#pragma unroll
+        for (int m = 0; m < NM; ++m)
+#pragma unroll
+            for (int t = 0; t < MMA_NW; ++t) bnext[m][t] = *reinterpret_cast<const uint4*>(wrow[m][t] + k0);
+        for (int kb = 0; kb < kn; kb += 32) {
+            uint4 b[NM][MMA_NW];
+#pragma unroll
+            for (int m = 0; m < NM; ++m)
+#pragma unroll
+                for (int t = 0; t < MMA_NW; ++t) {
+                    b[m][t] = bnext[m][t];
+                    if (kb + 32 < kn) bnext[m][t] = *reinterpret_cast<const uint4*>(wrow[m][t] + k0 + kb + 32);
+                }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const uint4 lo = *reinterpret_cast<const uint4*>(xs + (size_t)(mt * 16 + g) * MMA_PITCH + kb + 8 * tg);
+                const uint4 hi = *reinterpret_cast<const uint4*>(xs + (size_t)(mt * 16 + g + 8) * MMA_PITCH + kb + 8 * tg);
+#pragma unroll
+                for (int m = 0; m < NM; ++m)
+#pragma unroll
+                    for (int t = 0; t < MMA_NW; ++t) {
+                        mma_bf16(acc[m][mt][t], lo.x, hi.x, lo.y, hi.y, b[m][t].x, b[m][t].y);
+                        mma_bf16(acc[m][mt][t], lo.z, hi.z, lo.w, hi.w, b[m][t].z, b[m][t].w);
+                    }
+            }
+        }
+    }
+}
+
+template <int MT>
+__global__ void __launch_bounds__(MMA_WARPS * 32)
+moe_gate_up_mma_kernel(const bf16* __restrict__ x, int W, const bf16* __restrict__ w_gu, int ff,
+                       const int* __restrict__ offsets, const int* __restrict__ perm, const float* __restrict__ sel_w,
+                       const int* __restrict__ tiles, const int* __restrict__ n_tiles, int top, int scale_input, int act,
+                       float limit, float alpha, bf16* __restrict__ hidden) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* xs = reinterpret_cast<bf16*>(smem_raw);
+    __shared__ int src_row[MT * 16];
+    __shared__ float src_w[MT * 16];
+    pdl_wait();
+    if ((int)blockIdx.x >= *n_tiles) return;
+    const int e = tiles[2 * blockIdx.x], p0 = tiles[2 * blockIdx.x + 1];
+    const int rows = min(MT * 16, offsets[e + 1] - p0);
+    const int col0 = blockIdx.y * MMA_COLS, n_cols = min(MMA_COLS, ff - col0);
+    for (int r = threadIdx.x; r < MT * 16; r += blockDim.x) {
+        const int entry = r < rows ? perm[p0 + r] : -1;
+        src_row[r] = entry < 0 ? -1 : entry / top;
+        src_w[r] = (entry < 0 || !scale_input) ? 1.f : sel_w[entry];
+    }
+    const bf16* wg = w_gu + (size_t)e * 2 * ff * W;
+    const bf16* const w2[2] = {wg, wg + (size_t)ff * W};
+    float acc[2][MT][MMA_NW][4] = {};
+    mma_tile_product<MT, 2>(w2, col0, n_cols, W, xs, acc, [&](int k0, int kn) {
+        for (int idx = threadIdx.x; idx < MT * 16 * (MMA_KC / 8); idx += blockDim.x) {
+            const int r = idx / (MMA_KC / 8), kk = (idx - r * (MMA_KC / 8)) * 8;
+            const int row = src_row[r];
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (row >= 0 && kk < kn) {
+                Vec16<bf16> in;
+                in.load(x + (size_t)row * W + k0 + kk);
+                in.unpack(v);
+                const float sw = src_w[r];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] *= sw;
+            }
+            Vec16<bf16>::store(xs + (size_t)r * MMA_PITCH + kk, v);
+        }
+    });
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int t = 0; t < MMA_NW; ++t)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int r = mt * 16 + g + (j >> 1) * 8, c = (warp * MMA_NW + t) * 8 + 2 * tg + (j & 1);
+                if (r < rows && c < n_cols)
+                    hidden[(size_t)(p0 + r) * ff + col0 + c] =
+                        __float2bfloat16_rn(gated(acc[0][mt][t][j], acc[1][mt][t][j], act, limit, alpha));
+            }
+}
+
+template <int MT>
+__global__ void __launch_bounds__(MMA_WARPS * 32)
+moe_down_mma_kernel(const bf16* __restrict__ hidden, int ff, const bf16* __restrict__ w_down, int W,
+                    const int* __restrict__ offsets, const int* __restrict__ perm, const float* __restrict__ sel_w,
+                    const int* __restrict__ tiles, const int* __restrict__ n_tiles, int scale_output,
+                    float* __restrict__ ys) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* xs = reinterpret_cast<bf16*>(smem_raw);
+    pdl_wait();
+    if ((int)blockIdx.x >= *n_tiles) return;
+    const int e = tiles[2 * blockIdx.x], p0 = tiles[2 * blockIdx.x + 1];
+    const int rows = min(MT * 16, offsets[e + 1] - p0);
+    const int col0 = blockIdx.y * MMA_COLS, n_cols = min(MMA_COLS, W - col0);
+    const bf16* const w1[1] = {w_down + (size_t)e * W * ff};
+    float acc[1][MT][MMA_NW][4] = {};
+    mma_tile_product<MT, 1>(w1, col0, n_cols, ff, xs, acc, [&](int k0, int kn) {
+        for (int idx = threadIdx.x; idx < MT * 16 * (MMA_KC / 8); idx += blockDim.x) {
+            const int r = idx / (MMA_KC / 8), kk = (idx - r * (MMA_KC / 8)) * 8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < rows && kk < kn) v = *reinterpret_cast<const uint4*>(hidden + (size_t)(p0 + r) * ff + k0 + kk);
+            *reinterpret_cast<uint4*>(xs + (size_t)r * MMA_PITCH + kk) = v;
+        }
+    });
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = mt * 16 + g + (j >> 1) * 8;
+            if (r >= rows) continue;
+            const int entry = perm[p0 + r];
+            const float sw = scale_output ? sel_w[entry] : 1.f;
+#pragma unroll
+            for (int t = 0; t < MMA_NW; ++t) {
+                const int c = (warp * MMA_NW + t) * 8 + 2 * tg + (j & 1);
+                if (c < n_cols) ys[(size_t)entry * W + col0 + c] = acc[0][mt][t][j] * sw;
+            }
+        }
+}
+
+inline bool mma_takes(int dtype, int K, const void* a, const void* b) {
+    return dtype == QNN_DT_BF16 && K % 32 == 0 && ((((uintptr_t)a | (uintptr_t)b) & 15) == 0);
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ ys, int top, const void* __restrict__ shared, int shared_dt,
                                    float* __restrict__ out, int W, size_t n) {
     pdl_wait();
@@ -258,10 +439,10 @@ QNN_API int qnn_moe_route(const void* x, int x_dt, const void* w_router, int w_d
                           int score_fn, int renorm, int* sel_e, float* sel_w, cudaStream_t st) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || top > MAX_TOP || W <= 0) return QNN_ERR_ARGUMENT;
-    const int warps = 4;
-    const size_t smem = (size_t)warps * E * sizeof(float);
+    const int warps = E >= 8 ? 8 : (E >= 4 ? 4 : 2);
+    const size_t smem = (size_t)E * sizeof(float);
     if (smem > 48 * 1024) return QNN_ERR_UNSUPPORTED;
-    const dim3 grid((T + warps - 1) / warps), block(warps * 32);
+    const dim3 grid(T), block(warps * 32);
 #define QNN_ROUTE(TX, TW)                                                                                         \
     launch_pdl(moe_route_kernel<TX, TW>, grid, block, smem, st, (const TX*)x, (const TW*)w_router, T, W, E, top,  \
                score_fn, renorm, sel_e, sel_w)
@@ -273,22 +454,48 @@ QNN_API int qnn_moe_route(const void* x, int x_dt, const void* w_router, int w_d
     QNN_LAUNCH_CHECK();
 }
 
-QNN_API int qnn_moe_max_tiles(int n_entries, int E) { return (n_entries + TILE_ROWS - 1) / TILE_ROWS + E; }
+// Rows of a tile: 16, or 64 where the experts get many rows each and the two matrices take the tensor-core kernel
+// (a tile's weights are then read once for four times the rows).
+QNN_API int qnn_moe_tile_rows(int n_entries, int E, int dtype, int W, int ff) {
+    const bool mma = dtype == QNN_DT_BF16 && W % 32 == 0 && ff % 32 == 0;
+    return (mma && n_entries >= 48 * E) ? 64 : TILE_ROWS;
+}
+QNN_API int qnn_moe_max_tiles(int n_entries, int E, int tile_rows) { return (n_entries + tile_rows - 1) / tile_rows + E; }
 
-QNN_API int qnn_moe_plan(const int* sel_e, int n, int E, int* offsets, int* perm, int* tiles, int* n_tiles,
+QNN_API int qnn_moe_plan(const int* sel_e, int n, int E, int tile_rows, int* offsets, int* perm, int* tiles, int* n_tiles,
                          cudaStream_t st) {
     if (n <= 0) return 0;
-    if (E <= 0 || (size_t)2 * E * sizeof(int) > 48 * 1024) return QNN_ERR_ARGUMENT;
-    launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), st, sel_e, n, E, offsets, perm, tiles,
-               n_tiles);
+    if (E <= 0 || (size_t)2 * E * sizeof(int) > 48 * 1024 || (tile_rows != 16 && tile_rows != 64)) return QNN_ERR_ARGUMENT;
+    launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), st, sel_e, n, E, tile_rows, offsets, perm,
+               tiles, n_tiles);
     QNN_LAUNCH_CHECK();
 }
 
 QNN_API int qnn_moe_gate_up(const void* x, int dtype, int W, const void* w_gu, int ff, const int* offsets, const int* perm,
-                            const float* sel_w, const int* tiles, const int* n_tiles, int max_tiles, int top,
-                            int scale_input, int act, float limit, float alpha, void* hidden, cudaStream_t st) {
+                            const float* sel_w, const int* tiles, const int* n_tiles, int max_tiles, int tile_rows,
+                            int top, int scale_input, int act, float limit, float alpha, void* hidden, cudaStream_t st) {
     if (max_tiles <= 0) return 0;
     if (W <= 0 || ff <= 0 || top <= 0) return QNN_ERR_ARGUMENT;
+    if (tile_rows != 16 && tile_rows != 64) return QNN_ERR_ARGUMENT;
+    if (mma_takes(dtype, W, x, w_gu)) {
+        const dim3 mgrid(max_tiles, (ff + MMA_COLS - 1) / MMA_COLS);
+        if (mgrid.y > 65535) return QNN_ERR_UNSUPPORTED;
+        const size_t smem = (size_t)tile_rows * MMA_PITCH * sizeof(bf16);
+        if (tile_rows == 64) {
+            static bool set = false;
+            if (!set) {
+                cudaFuncSetAttribute(moe_gate_up_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                set = true;
+            }
+            launch_pdl(moe_gate_up_mma_kernel<4>, mgrid, dim3(MMA_WARPS * 32), smem, st, (const bf16*)x, W, (const bf16*)w_gu,
+                       ff, offsets, perm, sel_w, tiles, n_tiles, top, scale_input, act, limit, alpha, (bf16*)hidden);
+        } else {
+            launch_pdl(moe_gate_up_mma_kernel<1>, mgrid, dim3(MMA_WARPS * 32), smem, st, (const bf16*)x, W, (const bf16*)w_gu,
+                       ff, offsets, perm, sel_w, tiles, n_tiles, top, scale_input, act, limit, alpha, (bf16*)hidden);
+        }
+        QNN_LAUNCH_CHECK();
+    }
+    if (tile_rows != TILE_ROWS) return QNN_ERR_ARGUMENT;
     const dim3 grid(max_tiles, (ff + TILE_COLS - 1) / TILE_COLS);
     if (grid.y > 65535) return QNN_ERR_UNSUPPORTED;
     if (dtype == QNN_DT_BF16)
@@ -302,9 +509,29 @@ QNN_API int qnn_moe_gate_up(const void* x, int dtype, int W, const void* w_gu, i
 
 QNN_API int qnn_moe_down(const void* hidden, int dtype, int ff, const void* w_down, int W, const int* offsets,
                          const int* perm, const float* sel_w, const int* tiles, const int* n_tiles, int max_tiles,
-                         int scale_output, float* ys, cudaStream_t st) {
+                         int tile_rows, int scale_output, float* ys, cudaStream_t st) {
     if (max_tiles <= 0) return 0;
     if (W <= 0 || ff <= 0) return QNN_ERR_ARGUMENT;
+    if (tile_rows != 16 && tile_rows != 64) return QNN_ERR_ARGUMENT;
+    if (mma_takes(dtype, ff, hidden, w_down)) {
+        const dim3 mgrid(max_tiles, (W + MMA_COLS - 1) / MMA_COLS);
+        if (mgrid.y > 65535) return QNN_ERR_UNSUPPORTED;
+        const size_t smem = (size_t)tile_rows * MMA_PITCH * sizeof(bf16);
+        if (tile_rows == 64) {
+            static bool set = false;
+            if (!set) {
+                cudaFuncSetAttribute(moe_down_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                set = true;
+            }
+            launch_pdl(moe_down_mma_kernel<4>, mgrid, dim3(MMA_WARPS * 32), smem, st, (const bf16*)hidden, ff,
+                       (const bf16*)w_down, W, offsets, perm, sel_w, tiles, n_tiles, scale_output, ys);
+        } else {
+            launch_pdl(moe_down_mma_kernel<1>, mgrid, dim3(MMA_WARPS * 32), smem, st, (const bf16*)hidden, ff,
+                       (const bf16*)w_down, W, offsets, perm, sel_w, tiles, n_tiles, scale_output, ys);
+        }
+        QNN_LAUNCH_CHECK();
+    }
+    if (tile_rows != TILE_ROWS) return QNN_ERR_ARGUMENT;
     const dim3 grid(max_tiles, (W + TILE_COLS - 1) / TILE_COLS);
     if (grid.y > 65535) return QNN_ERR_UNSUPPORTED;
     if (dtype == QNN_DT_BF16)

@@ -69,27 +69,37 @@ __global__ void scale_heads_kernel(void* __restrict__ x, int dt, const float* __
     store_from_f(x, dt, i, load_as_f(x, dt, i) * (1.f / (1.f + expf(-g))));
 }
 
+// What becomes of a sum: itself; or, with a bias and 1/tau, the decay sigmoid(sum + bias[n])^(1/tau), formed as
+// exp(log_sigmoid(.) / tau) with the accurate exponential and logarithm.
+__device__ __forceinline__ float finish(float d, const void* bias, int bias_dt, float inv_tau, int n) {
+    if (bias == nullptr) return d;
+    const float z = d + load_as_f(bias, bias_dt, n);
+    return expf(inv_tau * (fminf(z, 0.f) - log1pf(expf(-fabsf(z)))));
+}
+
 // out[t, n] = x[t, :] . w[n, :], float32 sums and float32 out, for the few outputs that feed float32 math
-// (gates, decay logits).  Long rows: a warp per row walks the outputs, lanes stride the inner size.
+// (gates, decay logits).  Long rows: a warp per output, lanes stride the inner size.
 template <typename TX, typename TW>
 __global__ void small_linear_warp_kernel(const TX* __restrict__ x, const TW* __restrict__ w, float* __restrict__ out,
-                                         int T, int N, int K) {
+                                         int N, int K, size_t total, const void* __restrict__ bias, int bias_dt,
+                                         float inv_tau) {
     pdl_wait();
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (t >= T) return;
-    const TX* xr = x + (size_t)t * K;
-    for (int n = 0; n < N; ++n) {
-        const TW* wr = w + (size_t)n * K;
-        float d = 0.f;
-        for (int i = lane; i < K; i += 32) d += to_f(xr[i]) * to_f(wr[i]);
-        d = warp_sum(d);
-        if (lane == 0) out[(size_t)t * N + n] = d;
-    }
+    const size_t i = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (i >= total) return;
+    const size_t t = i / N;
+    const TX* xr = x + t * K;
+    const TW* wr = w + (i - t * N) * K;
+    float d = 0.f;
+    for (int k = lane; k < K; k += 32) d += to_f(xr[k]) * to_f(wr[k]);
+    d = warp_sum(d);
+    if (lane == 0) out[i] = finish(d, bias, bias_dt, inv_tau, (int)(i - t * N));
 }
 // Short rows: a thread per output.
 template <typename TX, typename TW>
 __global__ void small_linear_thread_kernel(const TX* __restrict__ x, const TW* __restrict__ w, float* __restrict__ out,
-                                           int N, int K, size_t total) {
+                                           int N, int K, size_t total, const void* __restrict__ bias, int bias_dt,
+                                           float inv_tau) {
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
@@ -99,7 +109,7 @@ __global__ void small_linear_thread_kernel(const TX* __restrict__ x, const TW* _
     const TW* wr = w + (size_t)n * K;
     float d = 0.f;
     for (int k = 0; k < K; ++k) d += to_f(xr[k]) * to_f(wr[k]);
-    out[i] = d;
+    out[i] = finish(d, bias, bias_dt, inv_tau, n);
 }
 
 inline int row_threads(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
@@ -139,17 +149,20 @@ QNN_API int qnn_scale_heads(void* x, int dt, const float* gate, int T, int H, in
     QNN_LAUNCH_CHECK();
 }
 
+// bias (may be null) and tau: out = sigmoid(x w^T + bias)^(1/tau) instead of x w^T.
 QNN_API int qnn_small_linear_f32(const void* x, int x_dt, const void* w, int w_dt, float* out, int T, int N, int K,
-                                 cudaStream_t st) {
+                                 const void* bias, int bias_dt, float tau, cudaStream_t st) {
     if (T <= 0 || N <= 0) return 0;
-    if (K <= 0) return QNN_ERR_ARGUMENT;
+    if (K <= 0 || (bias != nullptr && !(tau > 0.f))) return QNN_ERR_ARGUMENT;
+    const float inv_tau = bias != nullptr ? 1.f / tau : 0.f;
+    const size_t total = (size_t)T * N;
 #define QNN_SL(TX, TW)                                                                                               \
-    if (K >= 64)                                                                                                     \
-        launch_pdl(small_linear_warp_kernel<TX, TW>, dim3((T + 3) / 4), dim3(128), 0, st, (const TX*)x, (const TW*)w, \
-                   out, T, N, K);                                                                                    \
+    if (K > 128)                                                                                                     \
+        launch_pdl(small_linear_warp_kernel<TX, TW>, dim3((unsigned)((total + 7) / 8)), dim3(256), 0, st,            \
+                   (const TX*)x, (const TW*)w, out, N, K, total, bias, bias_dt, inv_tau);                            \
     else                                                                                                             \
-        launch_pdl(small_linear_thread_kernel<TX, TW>, dim3((unsigned)(((size_t)T * N + 255) / 256)), dim3(256), 0,  \
-                   st, (const TX*)x, (const TW*)w, out, N, K, (size_t)T * N);
+        launch_pdl(small_linear_thread_kernel<TX, TW>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st,      \
+                   (const TX*)x, (const TW*)w, out, N, K, total, bias, bias_dt, inv_tau);
     if (x_dt == QNN_DT_BF16 && w_dt == QNN_DT_BF16) { QNN_SL(bf16, bf16) }
     else if (x_dt == QNN_DT_BF16) { QNN_SL(bf16, float) }
     else if (w_dt == QNN_DT_BF16) { QNN_SL(float, bf16) }

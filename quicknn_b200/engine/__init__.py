@@ -5,7 +5,7 @@ from .generate import GenerationBackend, GenerationResult, PromptError, generate
 from .llm import LLM, Conversation
 from .model import Model, as_dtype
 from ..kernels.lib import KernelError, NonFiniteLogits
-from .profile import StepProfiler
+from .profile import OpTimer, StepProfiler
 
 __all__ = ["StepBatch", "Engine", "StepError", "GenerationBackend", "GenerationResult", "PromptError",
-           "generate", "plan_batches", "LLM", "Conversation", "Model", "as_dtype", "KernelError", "NonFiniteLogits", "StepProfiler"]
+           "generate", "plan_batches", "LLM", "Conversation", "Model", "as_dtype", "KernelError", "NonFiniteLogits", "StepProfiler", "OpTimer"]

@@ -69,10 +69,12 @@ class StepProfiler:
         self._graphs, eng.use_graphs = eng.use_graphs, False
         for blk in model.blocks:
             self._patch(blk.mixer, "forward", "mixer")
-            self._patch(blk.ff, "forward", "feed-forward")
+            if blk.ff is not None:
+                self._patch(blk.ff, "forward", "feed-forward")
         self._patch(RMSNorm, "__call__", "norms and residual")
         self._patch(RMSNorm, "add_to", "norms and residual")
         self._patch(ops, "add_", "norms and residual")
+        self._patch(ops, "add_scaled_rmsnorm", "norms and residual")
         self._patch(ops, "embed", "embedding")
         self._patch(ops, "embed_rmsnorm", "embedding")
         self._patch(model, "logits_of_rows", "head")
@@ -152,3 +154,133 @@ class _Missing:
 
 
 _MISSING = _Missing()
+
+
+# ---- time and roofline by kernel wrapper ------------------------------------------------------------------
+
+def _nbytes(t) -> int:
+    return t.numel() * t.element_size() if isinstance(t, torch.Tensor) else 0
+
+
+def _tensors(xs):
+    for x in xs:
+        if isinstance(x, torch.Tensor):
+            yield x
+        elif isinstance(x, (tuple, list)):
+            yield from _tensors(x)
+
+
+class OpTimer:
+    """Brackets every call of the kernel wrappers in ``kernels.ops`` with CUDA events while steps run eagerly, and
+    sets each wrapper's time against the least time its work could take: the bytes it has to move at ``hbm_gbs``
+    or its floating-point operations at ``tflops``, whichever is longer.  Bytes are those of the tensors that go
+    in and come out, except where a wrapper reads a part of its arguments only (decode attention reads the live
+    keys, not the pool; routed experts read the chosen experts' matrices); operations are counted for products,
+    attention, the linear-attention scan and the experts.  ``context`` is the number of cached positions that a
+    decode step's attention walks (the timer cannot see lengths that live on the device); prompts are taken to
+    be one sequence per step.
+
+        with OpTimer(engine, hbm_gbs=6500, tflops=1600, context=4096) as t:
+            engine.step(...)
+        for row in t.rows(): print(row)
+    """
+
+    SKIP = {"status_words", "finite_flag", "raise_on_status", "check_gemm_status", "wait_status_message", "dt_code",
+            "attention_refusal", "linear_refusal", "sample_scratch_bytes", "head_candidates", "head_argmax_fusable",
+            "qkv_rope_cache_fusable", "cache_append", "gemm_tcgen05", "gemm_skinny_tcgen05"}
+
+    def __init__(self, engine, hbm_gbs: float, tflops: float, context: int = 0):
+        self.engine, self.hbm, self.tflops, self.context = engine, hbm_gbs * 1e9, tflops * 1e12, context
+        self._undo: List[Tuple[str, object]] = []
+        self._recs: List[tuple] = []
+        self._depth = 0
+        self._graphs: Optional[bool] = None
+
+    def _cost(self, name: str, a, kw, out) -> Tuple[float, float]:
+        """(bytes, floating-point operations) of one call."""
+        byts = float(sum(_nbytes(t) for t in _tensors(a)) + sum(_nbytes(t) for t in _tensors(kw.values()))
+                     + sum(_nbytes(t) for t in _tensors([out])))
+        flops = 0.0
+        if name == "linear":
+            x, w = a[0], a[1]
+            flops = 2.0 * x.shape[0] * w.shape[0] * w.shape[1]
+        elif name == "small_linear_f32":
+            flops = 2.0 * a[0].shape[0] * a[1].shape[0] * a[1].shape[1]
+        elif name == "attn_prefill":
+            qkv, nq, nkv, hd, window = a[0], a[1], a[2], a[3], a[8]
+            T = qkv.shape[0]
+            keys = sum(min(p + 1, window) if window else p + 1 for p in range(T))
+            flops = 4.0 * nq * hd * keys
+        elif name == "attn_decode":
+            qkv, nq, nkv, hd, k_pool, v_pool, window = a[0], a[1], a[2], a[3], a[4], a[5], a[13]
+            seen = min(self.context, window) if window else self.context
+            pools = 1 if v_pool.data_ptr() == k_pool.data_ptr() else 2
+            byts = float(qkv.shape[0] * seen * nkv * hd * k_pool.element_size() * pools + _nbytes(qkv) + _nbytes(out))
+            flops = 4.0 * qkv.shape[0] * nq * hd * seen
+        elif name == "gla_scan":
+            proj, n_seqs, H, dim, vdim = a[0], a[10], a[11], a[12], a[13]
+            T = proj.shape[0]
+            flops = 4.0 * T * H * dim * vdim
+            byts = float(T * (2 * H * dim + H * vdim) * proj.element_size() + T * H * dim * 4 + T * H * vdim * 4
+                         + 2 * n_seqs * H * dim * vdim * 4)
+        elif name == "moe_experts":
+            x, top, wgu, wd = a[0], a[3], a[4], a[5]
+            T, W = x.shape
+            E, ff2, _ = wgu.shape
+            used = min(E, T * top)
+            flops = 2.0 * T * top * (ff2 + ff2 // 2) * W
+            byts = float(used * (ff2 + ff2 // 2) * W * wgu.element_size() + _nbytes(x) + _nbytes(out))
+        elif name in ("rope_cache_write",):
+            byts = float(2 * _nbytes(a[0]))
+        elif name.startswith("embed"):               # the rows that are looked up, not the table
+            byts = float(2 * sum(_nbytes(t) for t in _tensors([out])))
+        return byts, flops
+
+    def _timed(self, name: str, fn):
+        def call(*a, **kw):
+            if self._depth:                      # a wrapper called from inside another: the outer one is counted
+                return fn(*a, **kw)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self._depth += 1
+            e0.record()
+            try:
+                out = fn(*a, **kw)
+            finally:
+                e1.record()
+                self._depth -= 1
+            self._recs.append((name, e0, e1) + self._cost(name, a, kw, out))
+            return out
+        return call
+
+    def __enter__(self) -> "OpTimer":
+        self._graphs, self.engine.use_graphs = self.engine.use_graphs, False
+        for name, fn in list(vars(ops).items()):
+            if callable(fn) and not name.startswith("_") and getattr(fn, "__module__", "") == ops.__name__ \
+                    and not isinstance(fn, type) and name not in self.SKIP:
+                self._undo.append((name, fn))
+                setattr(ops, name, self._timed(name, fn))
+        return self
+
+    def __exit__(self, *exc) -> None:
+        for name, fn in self._undo:
+            setattr(ops, name, fn)
+        self._undo.clear()
+        self.engine.use_graphs = self._graphs
+        torch.cuda.synchronize(self.engine.device)
+
+    def rows(self) -> List[Dict[str, object]]:
+        """One record per wrapper, the costliest first: calls, milliseconds, the least milliseconds its bytes and
+        operations allow, and the quotient (1.0 = at the roofline)."""
+        torch.cuda.synchronize(self.engine.device)
+        agg: Dict[str, List[float]] = {}
+        for name, e0, e1, byts, flops in self._recs:
+            r = agg.setdefault(name, [0, 0.0, 0.0, 0.0, 0.0])
+            r[0] += 1
+            r[1] += e0.elapsed_time(e1)
+            r[2] += max(byts / self.hbm, flops / self.tflops) * 1e3
+            r[3] += byts
+            r[4] += flops
+        out = [{"op": k, "calls": int(v[0]), "ms": round(v[1], 4), "least_ms": round(v[2], 4),
+                "of_roofline": round(v[2] / v[1], 4) if v[1] > 0 else None, "gb": round(v[3] / 1e9, 4),
+                "gflop": round(v[4] / 1e9, 2)} for k, v in agg.items()]
+        return sorted(out, key=lambda r: -r["ms"])

@@ -67,16 +67,17 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_rmsnorm_strided": [c_vp, c_int, c_ll, c_vp, c_int, c_float, c_vp, c_int, c_ll, c_vp, c_ll, c_int, c_int, c_vp],
     "qnn_copy_rows": [c_vp, c_int, c_ll, c_vp, c_ll, c_int, c_int, c_vp],
     "qnn_scale_heads": [c_vp, c_int, c_vp, c_int, c_int, c_int, c_vp],
-    "qnn_small_linear_f32": [c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_int, c_vp],
-    "qnn_gla_scan": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_vp, c_int, c_float, c_float, c_vp, c_vp, c_vp, c_vp,
+    "qnn_small_linear_f32": [c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_int, c_vp, c_int, c_float, c_vp],
+    "qnn_gla_scan": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_float, c_vp, c_vp, c_vp, c_vp,
                      c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp],
     "qnn_gla_norm_gate": [c_vp, c_ll, c_vp, c_int, c_float, c_vp, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp],
     "qnn_moe_route": [c_vp, c_int, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp],
-    "qnn_moe_max_tiles": [c_int, c_int],
-    "qnn_moe_plan": [c_vp, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp],
-    "qnn_moe_gate_up": [c_vp, c_int, c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int,
+    "qnn_moe_tile_rows": [c_int, c_int, c_int, c_int, c_int],
+    "qnn_moe_max_tiles": [c_int, c_int, c_int],
+    "qnn_moe_plan": [c_vp, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp],
+    "qnn_moe_gate_up": [c_vp, c_int, c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int,
                         c_float, c_float, c_vp, c_vp],
-    "qnn_moe_down": [c_vp, c_int, c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp, c_vp],
+    "qnn_moe_down": [c_vp, c_int, c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp],
     "qnn_moe_combine": [c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_vp],
     "qnn_gated_act_clamped": [c_vp, c_vp, c_int, c_int, c_int, c_float, c_float, c_vp],
 }

@@ -857,36 +857,42 @@ def scale_heads(x: torch.Tensor, gate_logits: torch.Tensor, n_heads: int) -> tor
     return x
 
 
-def small_linear_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def small_linear_f32(x: torch.Tensor, w: torch.Tensor, decay_bias: Optional[torch.Tensor] = None,
+                     tau: Optional[float] = None) -> torch.Tensor:
     """x w^T with float32 sums and a float32 result, whatever the element types: for the few outputs that feed
-    float32 math (a gate per head, decay logits).  A plain kernel; the order of a sum depends on the inner size only."""
+    float32 math (a gate per head, decay logits).  With ``decay_bias`` and ``tau`` the result is the decay
+    sigmoid(x w^T + bias)^(1/tau) itself.  A plain kernel; the order of a sum depends on the inner size only."""
     _req(x, "x", None, 2)
     _req(w, "w", None, 2)
     T, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
         raise ValueError(f"small_linear_f32: x is [*, {K}] but w is [*, {w.shape[1]}]")
+    if decay_bias is not None:
+        _req(decay_bias, "decay_bias", None, 1)
+        if decay_bias.numel() != N or tau is None or not tau > 0:
+            raise ValueError("small_linear_f32: a decay needs one bias per output and a positive tau")
     out = torch.empty((T, N), dtype=torch.float32, device=x.device)
-    _lib.check(_lib.load().qnn_small_linear_f32(_p(x), dt_code(x), _p(w), dt_code(w), _p(out), T, N, K, _stream()),
-               "small_linear_f32")
+    _lib.check(_lib.load().qnn_small_linear_f32(_p(x), dt_code(x), _p(w), dt_code(w), _p(out), T, N, K, _p(decay_bias),
+                                                dt_code(decay_bias) if decay_bias is not None else 0,
+                                                float(tau or 0.0), _stream()), "small_linear_f32")
     return out
 
 
 # ---- gated linear attention -------------------------------------------------------------------------------
 
-def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, bias: torch.Tensor, tau: float,
-             q_scale: float, seq_row0: Optional[torch.Tensor], seq_len: Optional[torch.Tensor], slots: torch.Tensor,
+def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, q_scale: float,
+             seq_row0: Optional[torch.Tensor], seq_len: Optional[torch.Tensor], slots: torch.Tensor,
              state: torch.Tensor, n_seqs: int, n_heads: int, dim: int, vdim: int) -> torch.Tensor:
-    """The recurrence S = diag(a) S + k v^T, o = S^T (q q_scale) with a = sigmoid(z + bias)^(1/tau), over the rows
-    of every sequence in order, from the state of the sequence's slot and back into it.  ``proj`` holds q and k
-    ([*, heads*dim]) and v ([*, heads*vdim]) from the given columns on; returns o, float32 [rows, heads*vdim]."""
+    """The recurrence S = diag(a) S + k v^T, o = S^T (q q_scale) over the rows of every sequence in order, from the
+    state of the sequence's slot and back into it.  ``proj`` holds q and k ([*, heads*dim]) and v ([*, heads*vdim])
+    from the given columns on; ``decay`` the decays a, float32 [rows, heads*dim]; returns o, float32 [rows, heads*vdim]."""
     _req(proj, "proj", None, 2)
-    _req(z, "z", torch.float32, 2)
-    _req(bias, "bias", None, 1)
+    _req(decay, "decay", torch.float32, 2)
     _req(slots, "slots", torch.int32, 1)
     _req(state, "state", torch.float32)
     T = proj.shape[0]
-    if tuple(z.shape) != (T, n_heads * dim) or bias.numel() != n_heads * dim or slots.numel() < n_seqs:
+    if tuple(decay.shape) != (T, n_heads * dim) or slots.numel() < n_seqs:
         raise ValueError("gla_scan: shapes do not agree")
     if tuple(state.shape[1:]) != (n_heads, dim, vdim):
         raise ValueError(f"gla_scan: the state is {tuple(state.shape)}, expected [slots, {n_heads}, {dim}, {vdim}]")
@@ -896,8 +902,8 @@ def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Te
         raise ValueError("gla_scan: fewer rows than sequences")
     out = torch.empty((T, n_heads * vdim), dtype=torch.float32, device=proj.device)
     _lib.check(_lib.load().qnn_gla_scan(
-        _col_ptr(proj, q_col), _col_ptr(proj, k_col), _col_ptr(proj, v_col), proj.shape[1], dt_code(proj), _p(z),
-        z.shape[1], _p(bias), dt_code(bias), float(tau), float(q_scale), _p(seq_row0), _p(seq_len), _p(slots), _p(state),
+        _col_ptr(proj, q_col), _col_ptr(proj, k_col), _col_ptr(proj, v_col), proj.shape[1], dt_code(proj), _p(decay),
+        decay.shape[1], float(q_scale), _p(seq_row0), _p(seq_len), _p(slots), _p(state),
         _p(out), out.shape[1], n_seqs, n_heads, dim, vdim, _stream()), "gla_scan")
     return out
 
@@ -958,18 +964,20 @@ def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: 
         raise ValueError("moe_experts: shapes do not agree")
     L = _lib.load()
     n = T * top
-    max_tiles = int(L.qnn_moe_max_tiles(n, E))
+    tile_rows = int(L.qnn_moe_tile_rows(n, E, dt_code(x), W, ff))       # 16, or 64 where experts get many rows each
+    max_tiles = int(L.qnn_moe_max_tiles(n, E, tile_rows))
     meta = torch.empty(E + 1 + n + 2 * max_tiles + 1, dtype=torch.int32, device=x.device)
     offsets, perm = meta[:E + 1], meta[E + 1:E + 1 + n]
     tiles, n_tiles = meta[E + 1 + n:E + 1 + n + 2 * max_tiles], meta[E + 1 + n + 2 * max_tiles:]
-    _lib.check(L.qnn_moe_plan(_p(sel_e), n, E, _p(offsets), _p(perm), _p(tiles), _p(n_tiles), _stream()), "moe_plan")
+    _lib.check(L.qnn_moe_plan(_p(sel_e), n, E, tile_rows, _p(offsets), _p(perm), _p(tiles), _p(n_tiles), _stream()),
+               "moe_plan")
     hidden = torch.empty((n, ff), dtype=x.dtype, device=x.device)
     _lib.check(L.qnn_moe_gate_up(_p(x), dt_code(x), W, _p(w_gate_up), ff, _p(offsets), _p(perm), _p(sel_w), _p(tiles),
-                                 _p(n_tiles), max_tiles, top, int(weight_on_input), int(activation), float(limit),
+                                 _p(n_tiles), max_tiles, tile_rows, top, int(weight_on_input), int(activation), float(limit),
                                  float(alpha), _p(hidden), _stream()), "moe_gate_up")
     ys = torch.empty((n, W), dtype=torch.float32, device=x.device)
     _lib.check(L.qnn_moe_down(_p(hidden), dt_code(x), ff, _p(w_down), W, _p(offsets), _p(perm), _p(sel_w), _p(tiles),
-                              _p(n_tiles), max_tiles, int(not weight_on_input), _p(ys), _stream()), "moe_down")
+                              _p(n_tiles), max_tiles, tile_rows, int(not weight_on_input), _p(ys), _stream()), "moe_down")
     if top == 1 and shared is None:
         return ys
     if shared is not None:

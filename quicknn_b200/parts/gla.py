@@ -9,7 +9,7 @@ The state lives in the cache's fixed-size state region, one [heads, dim, vdim] f
 when the slot is handed out; the mixer needs no keys or values.  A step walks each sequence's rows in order from
 the slot's state and leaves the new state there, so whole prompts, portions and single tokens are one kernel.
 q, k, v and the gate are one stacked product; the decay's logits are formed in float32 from the low-rank
-projection's output, and the decay itself (log-sigmoid, division by tau, exponential) inside the scan.
+projection's output, and the decay itself (log-sigmoid, division by tau, exponential) in the same kernel's epilogue.
 """
 from __future__ import annotations
 
@@ -76,8 +76,8 @@ class GatedLinearAttention(Mixer):
     def forward(self, x: torch.Tensor, step, line) -> torch.Tensor:
         H, d, vd = self.n_heads, self.dim, self.vdim
         p = project(x, self.w_in)                                         # q | k | v | gate
-        z = ops.small_linear_f32(project(x, self.w_a1), self.w_a2)        # decay logits, float32
-        o = ops.gla_scan(p, 0, H * d, 2 * H * d, z, self.bias, self.tau, float(d) ** -0.5,
+        a = ops.small_linear_f32(project(x, self.w_a1), self.w_a2, self.bias, self.tau)     # the decays, float32
+        o = ops.gla_scan(p, 0, H * d, 2 * H * d, a, float(d) ** -0.5,
                          None if step.mode == "decode" else step.seq_row0,
                          None if step.mode == "decode" else step.seq_len,
                          step.slots, line.state, step.n_seqs, H, d, vd)

@@ -315,9 +315,12 @@ def test_latent_attention_alone_and_a_window_one_token_off_would_show(dtype, kv_
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,top,shared", [(5, 1, None), (6, 2, (24, 1.1)), (3, 3, None), (40, 4, (8, 0.4))])
-def test_routed_experts_alone(dtype, experts, top, shared):
+@pytest.mark.parametrize("W,ff", [(72, 40), (128, 64), (320, 96)])
+def test_routed_experts_alone(dtype, experts, top, shared, W, ff):
+    """Widths in whole blocks of 32 take the tensor-core tiles in bfloat16 (16 rows, and 64 where the experts get many
+    rows each), other widths and float32 the plain tiles; (320, 96): more than one block of inner elements."""
     from quicknn_b200.parts import FEED_FORWARDS, PartSpec
-    W, ff, limit = 72, 40, 0.35
+    limit = 0.35
     sh = None if shared is None else PartSpec("clamped_mlp", {"hidden_size": W, "intermediate_size": shared[0],
                                                               "limit": shared[1]})
     spec = PartSpec("routed_experts", {"hidden_size": W, "experts": experts, "top": top, "intermediate_size": ff,
@@ -341,7 +344,7 @@ def test_routed_experts_alone(dtype, experts, top, shared):
     mlp = {"router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": limit},
            "shared": None if shared is None else {"ff": shared[0], "limit": shared[1]}}
     w64 = {k: v.astype(np.float64) for k, v in w.items()}
-    for rows in (1, 3, 150):                   # fewer rows than experts, tiles that are not full, many tiles
+    for rows in (1, 3, 150, 700):              # fewer rows than experts, tiles that are not full, many tiles, large tiles
         x = bf(rnd((rows, W), 200 + rows))
         got = host(part.forward(dev(x, dtype), None))
         ref = FP.routed_ff(x.astype(np.float64), w64, mlp)
