@@ -9,57 +9,72 @@
 //                       into it: whole prompts, portions and single tokens are the same launch
 //   qnn_gla_norm_gate   per head: RMS norm of o over vdim with a weight shared by the heads, times silu(g)
 //
-// The scan: a block owns 32 value columns of one (sequence, head).  Four lanes share a column, each with a quarter of
-// the key channels of the state in registers; q, k, the decay and v of 16 rows at a time are staged in shared memory,
-// the next 16 rows' loads in flight while these are walked; a lane reads its channels as 16-byte pieces.  The
-// order of the sums depends on dim only, so a row gives the same numbers in any batch and any cutting of its sequence.
+// The scan: a block owns 64 (32 with more than 128 key channels) value columns of one (sequence, head).  Eight lanes
+// share a group of 4 (2) columns, each with an eighth of the key channels of the state in registers, so that what a
+// lane reads of q, k and the decay from shared memory serves several columns (with one column per lane the kernel
+// was bound by shared-memory bandwidth: every column read the same 1.5 KB per row).  q, k, the decay and v of 16 rows
+// at a time are staged in shared memory, the next 16 rows' loads in flight while these are walked.  The order of
+// the sums depends on dim only, so a row gives the same numbers in any batch and any cutting of its sequence.
 #include "common.cuh"
 
 using namespace qnn;
 
 namespace {
 
-constexpr int GLA_COLS = 32;      // value columns of a block
-constexpr int GLA_SHARE = 4;      // lanes that share a column
+constexpr int GLA_SHARE = 8;      // lanes that share a group of columns, each with an eighth of the key channels
 constexpr int GLA_ROWS = 16;      // rows staged at a time
-constexpr int GLA_THREADS = GLA_COLS * GLA_SHARE;
+constexpr int GLA_THREADS = 128;
+constexpr int GLA_GROUPS = GLA_THREADS / GLA_SHARE;      // column groups of a block
 
 // One chunk of GLA_ROWS rows in shared memory: q, k, decay as [row][part][channel of the part] with a pad of 4 floats
-// between the parts (the four lanes of a column read 16 bytes each from four different banks), then v [row][column].
-template <int RPT>
+// between the parts (the eight lanes of a column group read 16 bytes each from eight different banks), then v
+// [row][column].  RPT: key channels per lane; CPT: value columns per lane.
+template <int RPT, int CPT>
 struct GlaChunk {
+    static constexpr int COLS = GLA_GROUPS * CPT;
     static constexpr int PART = RPT + 4, ROW = GLA_SHARE * PART, ARRAY = GLA_ROWS * ROW;
-    static constexpr int FLOATS = 3 * ARRAY + GLA_ROWS * GLA_COLS;
+    static constexpr int FLOATS = 3 * ARRAY + GLA_ROWS * COLS;
     static constexpr int PER_THREAD = GLA_ROWS * RPT * GLA_SHARE / GLA_THREADS;      // staged elements of one array per thread
-    static constexpr int V_PER_THREAD = GLA_ROWS * GLA_COLS / GLA_THREADS;
+    static constexpr int V_PER_THREAD = GLA_ROWS * COLS / GLA_THREADS;
 };
 
-template <typename T, int RPT>
+template <typename T, int RPT, int CPT>
 __global__ void __launch_bounds__(GLA_THREADS)
 gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long ld,
                 const float* __restrict__ decay, long long ldd, float q_scale, const int* __restrict__ seq_row0,
                 const int* __restrict__ seq_len, const int* __restrict__ slots, float* __restrict__ state,
-                float* __restrict__ out, long long ldo, int H, int dim, int vdim) {
-    using C = GlaChunk<RPT>;
+                float* __restrict__ out, long long ldo, int H, int dim, int vdim, int seg_len, int nseg) {
+    using C = GlaChunk<RPT, CPT>;
     constexpr int DIMP = RPT * GLA_SHARE;                    // key channels with padding
-    constexpr bool AHEAD = RPT <= 32;                        // the next chunk's loads in registers while this one is walked
+    constexpr bool AHEAD = RPT <= 16;                        // the next chunk's loads in registers while this one is walked
     extern __shared__ __align__(16) float sm[];
-    const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * GLA_COLS;
+    const int h = blockIdx.y, c0 = blockIdx.x * C::COLS;
     pdl_wait();
-    const int slot = slots[b];
-    const int row0 = seq_row0 ? seq_row0[b] : b;
-    const int n = seq_len ? seq_len[b] : 1;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int part = lane & (GLA_SHARE - 1), cl = warp * (32 / GLA_SHARE) + (lane >> 2);
-    const int col = c0 + cl;
-    const bool live = slot >= 0 && col < vdim;
-    float S[RPT];
+    // whole sequences: block z walks sequence z from its slot's state.  Segments (seg_len > 0): block z walks segment
+    // z % nseg of sequence z / nseg, rows seg * seg_len .. of it, from and into entry z of `state` (a scratch)
+    int slot, row0, n;
+    if (seg_len > 0) {
+        const int b = blockIdx.z / nseg, seg = blockIdx.z - b * nseg;
+        const int len = seq_len ? seq_len[b] : 1;
+        slot = slots[b] >= 0 ? (int)blockIdx.z : -1;
+        row0 = (seq_row0 ? seq_row0[b] : b) + seg * seg_len;
+        n = max(0, min(seg_len, len - seg * seg_len));
+    } else {
+        slot = slots[blockIdx.z];
+        row0 = seq_row0 ? seq_row0[blockIdx.z] : blockIdx.z;
+        n = seq_len ? seq_len[blockIdx.z] : 1;
+    }
+    const int part = threadIdx.x & (GLA_SHARE - 1), grp = threadIdx.x / GLA_SHARE;
+    const int col = c0 + grp * CPT;                          // the first of this lane's columns
+    float S[RPT][CPT];
     float* my_state = state + (((size_t)(slot < 0 ? 0 : slot) * H + h) * dim) * vdim + col;
 #pragma unroll
-    for (int r = 0; r < RPT; ++r) {
-        const int i = part * RPT + r;
-        S[r] = (live && i < dim) ? my_state[(size_t)i * vdim] : 0.f;
-    }
+    for (int r = 0; r < RPT; ++r)
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            const int i = part * RPT + r;
+            S[r][c] = (slot >= 0 && i < dim && col + c < vdim) ? my_state[(size_t)i * vdim + c] : 0.f;
+        }
     float rq[C::PER_THREAD], rk[C::PER_THREAD], ra[C::PER_THREAD], rv[C::V_PER_THREAD];
     auto fetch = [&](int t0) {                               // global memory -> registers (rows beyond the sequence: nothing)
         const int nt = min(GLA_ROWS, n - t0);
@@ -76,7 +91,7 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
         }
 #pragma unroll
         for (int e = 0; e < C::V_PER_THREAD; ++e) {
-            const int idx = threadIdx.x + e * GLA_THREADS, tt = idx / GLA_COLS, c = idx - tt * GLA_COLS;
+            const int idx = threadIdx.x + e * GLA_THREADS, tt = idx / C::COLS, c = idx - tt * C::COLS;
             rv[e] = (tt < nt && c0 + c < vdim) ? to_f(v[(size_t)(row0 + t0 + tt) * ld + h * vdim + c0 + c]) : 0.f;
         }
     };
@@ -102,26 +117,36 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
         float* buf = sm + (AHEAD ? cur * C::FLOATS : 0);
         if (AHEAD && more) fetch(t0 + GLA_ROWS);
         for (int tt = 0; tt < nt; ++tt) {
-            const float vj = buf[3 * C::ARRAY + tt * GLA_COLS + cl];
+            float vj[CPT], acc[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                vj[c] = buf[3 * C::ARRAY + tt * C::COLS + grp * CPT + c];
+                acc[c] = 0.f;
+            }
             const float4* aq = reinterpret_cast<const float4*>(buf + tt * C::ROW + part * C::PART);
             const float4* ak = reinterpret_cast<const float4*>(buf + C::ARRAY + tt * C::ROW + part * C::PART);
             const float4* aa = reinterpret_cast<const float4*>(buf + 2 * C::ARRAY + tt * C::ROW + part * C::PART);
-            float acc = 0.f;
 #pragma unroll
             for (int j = 0; j < RPT / 4; ++j) {
                 const float4 a4 = aa[j], k4 = ak[j], q4 = aq[j];
-                S[4 * j] = a4.x * S[4 * j] + k4.x * vj;
-                acc += S[4 * j] * q4.x;
-                S[4 * j + 1] = a4.y * S[4 * j + 1] + k4.y * vj;
-                acc += S[4 * j + 1] * q4.y;
-                S[4 * j + 2] = a4.z * S[4 * j + 2] + k4.z * vj;
-                acc += S[4 * j + 2] * q4.z;
-                S[4 * j + 3] = a4.w * S[4 * j + 3] + k4.w * vj;
-                acc += S[4 * j + 3] * q4.w;
+                const float av[4] = {a4.x, a4.y, a4.z, a4.w}, kv[4] = {k4.x, k4.y, k4.z, k4.w};
+                const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int c = 0; c < CPT; ++c) {
+                        S[4 * j + u][c] = av[u] * S[4 * j + u][c] + kv[u] * vj[c];
+                        acc[c] += S[4 * j + u][c] * qv[u];
+                    }
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (part == 0 && col < vdim) out[(size_t)(row0 + t0 + tt) * ldo + h * vdim + col] = slot >= 0 ? acc : 0.f;
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 1);
+                acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 2);
+                acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 4);
+                if (out != nullptr && part == 0 && col + c < vdim)
+                    out[(size_t)(row0 + t0 + tt) * ldo + h * vdim + col + c] = slot >= 0 ? acc[c] : 0.f;
+            }
         }
         if (more) {
             if (AHEAD) {
@@ -135,13 +160,58 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
             __syncthreads();
         }
     }
-    if (live) {
+    if (slot >= 0) {
 #pragma unroll
-        for (int r = 0; r < RPT; ++r) {
-            const int i = part * RPT + r;
-            if (i < dim) my_state[(size_t)i * vdim] = S[r];
-        }
+        for (int r = 0; r < RPT; ++r)
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const int i = part * RPT + r;
+                if (i < dim && col + c < vdim) my_state[(size_t)i * vdim + c] = S[r][c];
+            }
     }
+}
+
+// ---- long prompts in segments ------------------------------------------------------------------------------------
+// The recurrence is linear in the state: over a segment of rows, S_end = D (.) S_start + L with D the product of the
+// segment's decays per key channel and L the state that the segment builds from nothing.  So a long sequence is cut
+// into segments of seg_len rows that run side by side: the scan once without outputs from empty states (L), the
+// decay products (D), a short pass over the segments in order that leaves every segment's start state in the scratch
+// and the sequence's new state in its slot, and the scan once more from those start states, with outputs.
+
+// D[z][c] = product of decay[rows of segment z][c]; a thread per (segment, channel)
+__global__ void gla_segment_decay_kernel(const float* __restrict__ decay, long long ldd, const int* __restrict__ seq_row0,
+                                         const int* __restrict__ seq_len, int seg_len, int nseg, float* __restrict__ D,
+                                         int HD) {
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, z = blockIdx.y;
+    if (c >= HD) return;
+    const int b = z / nseg, seg = z - b * nseg;
+    const int row0 = seq_row0[b] + seg * seg_len, n = max(0, min(seg_len, seq_len[b] - seg * seg_len));
+    float d = 1.f;
+    for (int t = 0; t < n; ++t) d *= decay[(size_t)(row0 + t) * ldd + c];
+    D[(size_t)z * HD + c] = d;
+}
+
+// scratch[z] holds L of segment z and gets the segment's start state; the slot's state moves on to the sequence's end.
+// A thread per state element of a sequence.
+__global__ void gla_segment_prefix_kernel(float* __restrict__ scratch, const float* __restrict__ D,
+                                          const int* __restrict__ slots, float* __restrict__ state, int nseg, int dim,
+                                          int vdim, size_t per_seq) {
+    pdl_wait();
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (e >= per_seq) return;
+    const int slot = slots[b];
+    if (slot < 0) return;
+    const size_t hi = e / vdim;                               // (head, key channel) = the decay's column
+    float carry = state[(size_t)slot * per_seq + e];
+    for (int seg = 0; seg < nseg; ++seg) {
+        const size_t z = (size_t)b * nseg + seg;
+        const float L = scratch[z * per_seq + e];
+        scratch[z * per_seq + e] = carry;
+        carry = D[z * (per_seq / vdim) + hi] * carry + L;
+    }
+    state[(size_t)slot * per_seq + e] = carry;
 }
 
 // a warp per (row, head)
@@ -167,25 +237,27 @@ __global__ void gla_norm_gate_kernel(const float* __restrict__ o, long long ldo,
 template <typename T>
 int scan_launch(const void* q, const void* k, const void* v, long long ld, const float* decay, long long ldd, float q_scale,
                 const int* seq_row0, const int* seq_len, const int* slots, float* state, float* out, long long ldo, int B,
-                int H, int dim, int vdim, cudaStream_t st) {
-    const dim3 grid((vdim + GLA_COLS - 1) / GLA_COLS, H, B);
+                int H, int dim, int vdim, int seg_len, int nseg, cudaStream_t st) {
     const int rpt = (dim + GLA_SHARE - 1) / GLA_SHARE;
-#define QNN_GLA(RPTV)                                                                                                \
+#define QNN_GLA(RPTV, CPTV)                                                                                          \
     {                                                                                                                \
-        const size_t smem = (size_t)GlaChunk<RPTV>::FLOATS * sizeof(float) * (RPTV <= 32 ? 2 : 1);                   \
+        using C = GlaChunk<RPTV, CPTV>;                                                                              \
+        const dim3 grid((vdim + C::COLS - 1) / C::COLS, H, seg_len > 0 ? B * nseg : B);                              \
+        const size_t smem = (size_t)C::FLOATS * sizeof(float) * (RPTV <= 16 ? 2 : 1);                                \
         static bool set = false;                                                                                     \
         if (smem > 48 * 1024 && !set) {                                                                              \
-            cudaFuncSetAttribute(gla_scan_kernel<T, RPTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+            cudaFuncSetAttribute(gla_scan_kernel<T, RPTV, CPTV>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                 (int)smem);                                                                         \
             set = true;                                                                                              \
         }                                                                                                            \
-        launch_pdl(gla_scan_kernel<T, RPTV>, grid, dim3(GLA_THREADS), smem, st, (const T*)q, (const T*)k,           \
-                   (const T*)v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, H, dim, vdim);   \
+        launch_pdl(gla_scan_kernel<T, RPTV, CPTV>, grid, dim3(GLA_THREADS), smem, st, (const T*)q, (const T*)k,     \
+                   (const T*)v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, H, dim, vdim,    \
+                   seg_len, nseg);                                                                                   \
     }
-    if (rpt <= 4) QNN_GLA(4)
-    else if (rpt <= 8) QNN_GLA(8)
-    else if (rpt <= 16) QNN_GLA(16)
-    else if (rpt <= 32) QNN_GLA(32)
-    else if (rpt <= 64) QNN_GLA(64)
+    if (rpt <= 4) QNN_GLA(4, 4)
+    else if (rpt <= 8) QNN_GLA(8, 4)
+    else if (rpt <= 16) QNN_GLA(16, 4)
+    else if (rpt <= 32) QNN_GLA(32, 2)
     else return QNN_ERR_UNSUPPORTED;
 #undef QNN_GLA
     QNN_LAUNCH_CHECK();
@@ -206,9 +278,37 @@ QNN_API int qnn_gla_scan(const void* q, const void* k, const void* v, long long 
     if ((seq_row0 == nullptr) != (seq_len == nullptr)) return QNN_ERR_ARGUMENT;
     if (dtype == QNN_DT_BF16)
         return scan_launch<bf16>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim,
-                                 vdim, st);
+                                 vdim, 0, 1, st);
     return scan_launch<float>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim, vdim,
-                              st);
+                              0, 1, st);
+}
+
+// The same for sequences of up to nseg * seg_len rows, in segments that run side by side (see above).  scratch:
+// [B * nseg, H, dim, vdim] float32, zeroed by the caller; seg_decay: [B * nseg, H * dim] float32.  Four launches.
+QNN_API int qnn_gla_scan_segments(const void* q, const void* k, const void* v, long long ld, int dtype, const float* decay,
+                                  long long ldd, float q_scale, const int* seq_row0, const int* seq_len, const int* slots,
+                                  float* state, float* out, long long ldo, int B, int H, int dim, int vdim, int seg_len,
+                                  int nseg, float* scratch, float* seg_decay, cudaStream_t st) {
+    if (B <= 0) return 0;
+    if (H <= 0 || dim <= 0 || vdim <= 0 || H > 65535 || seg_len < 1 || nseg < 1 || (long long)B * nseg > 65535)
+        return QNN_ERR_ARGUMENT;
+    if (seq_row0 == nullptr || seq_len == nullptr) return QNN_ERR_ARGUMENT;
+    int rc;
+#define QNN_SCAN(STATE, OUT)                                                                                           \
+    (dtype == QNN_DT_BF16 ? scan_launch<bf16>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, STATE, OUT, ldo, \
+                                              B, H, dim, vdim, seg_len, nseg, st)                                      \
+                          : scan_launch<float>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, STATE, OUT, \
+                                               ldo, B, H, dim, vdim, seg_len, nseg, st))
+    if ((rc = QNN_SCAN(scratch, nullptr)) != 0) return rc;
+    const int HD = H * dim;
+    launch_pdl(gla_segment_decay_kernel, dim3((HD + 127) / 128, B * nseg), dim3(128), 0, st, decay, ldd, seq_row0, seq_len,
+               seg_len, nseg, seg_decay, HD);
+    const size_t per_seq = (size_t)H * dim * vdim;
+    launch_pdl(gla_segment_prefix_kernel, dim3((unsigned)((per_seq + 255) / 256), B), dim3(256), 0, st, scratch,
+               (const float*)seg_decay, slots, state, nseg, dim, vdim, per_seq);
+    if ((rc = (int)cudaGetLastError()) != 0) return rc;
+    return QNN_SCAN(scratch, out);
+#undef QNN_SCAN
 }
 
 QNN_API int qnn_gla_norm_gate(const float* o, long long ldo, const void* w, int w_dt, float eps, const void* g,

@@ -95,21 +95,31 @@ __global__ void small_linear_warp_kernel(const TX* __restrict__ x, const TW* __r
     d = warp_sum(d);
     if (lane == 0) out[i] = finish(d, bias, bias_dt, inv_tau, (int)(i - t * N));
 }
-// Short rows: a thread per output.
+// Short rows: a thread per output; a block owns 8 rows x 32 outputs and reads their inner elements through shared
+// memory (the weight rows of neighbouring outputs lie K elements apart: read directly, every load of a warp
+// would touch 32 lines).
+constexpr int SL_ROWS = 8, SL_OUTS = 32, SL_MAXK = 128;
 template <typename TX, typename TW>
-__global__ void small_linear_thread_kernel(const TX* __restrict__ x, const TW* __restrict__ w, float* __restrict__ out,
-                                           int N, int K, size_t total, const void* __restrict__ bias, int bias_dt,
-                                           float inv_tau) {
+__global__ void __launch_bounds__(SL_ROWS * SL_OUTS)
+small_linear_thread_kernel(const TX* __restrict__ x, const TW* __restrict__ w, float* __restrict__ out, int T, int N, int K,
+                           const void* __restrict__ bias, int bias_dt, float inv_tau) {
+    __shared__ float xs[SL_ROWS][SL_MAXK], ws[SL_OUTS][SL_MAXK + 1];
     pdl_wait();
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= total) return;
-    const size_t t = i / N;
-    const int n = (int)(i - t * N);
-    const TX* xr = x + t * K;
-    const TW* wr = w + (size_t)n * K;
+    const int t0 = blockIdx.y * SL_ROWS, n0 = blockIdx.x * SL_OUTS;
+    for (int idx = threadIdx.x; idx < SL_ROWS * K; idx += blockDim.x) {
+        const int r = idx / K, kk = idx - r * K;
+        xs[r][kk] = t0 + r < T ? to_f(x[(size_t)(t0 + r) * K + kk]) : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < SL_OUTS * K; idx += blockDim.x) {
+        const int c = idx / K, kk = idx - c * K;
+        ws[c][kk] = n0 + c < N ? to_f(w[(size_t)(n0 + c) * K + kk]) : 0.f;
+    }
+    __syncthreads();
+    const int r = threadIdx.x / SL_OUTS, c = threadIdx.x % SL_OUTS;
+    if (t0 + r >= T || n0 + c >= N) return;
     float d = 0.f;
-    for (int k = 0; k < K; ++k) d += to_f(xr[k]) * to_f(wr[k]);
-    out[i] = finish(d, bias, bias_dt, inv_tau, n);
+    for (int kk = 0; kk < K; ++kk) d += xs[r][kk] * ws[c][kk];
+    out[(size_t)(t0 + r) * N + n0 + c] = finish(d, bias, bias_dt, inv_tau, n0 + c);
 }
 
 inline int row_threads(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
@@ -157,12 +167,12 @@ QNN_API int qnn_small_linear_f32(const void* x, int x_dt, const void* w, int w_d
     const float inv_tau = bias != nullptr ? 1.f / tau : 0.f;
     const size_t total = (size_t)T * N;
 #define QNN_SL(TX, TW)                                                                                               \
-    if (K > 128)                                                                                                     \
+    if (K > SL_MAXK)                                                                                                 \
         launch_pdl(small_linear_warp_kernel<TX, TW>, dim3((unsigned)((total + 7) / 8)), dim3(256), 0, st,            \
                    (const TX*)x, (const TW*)w, out, N, K, total, bias, bias_dt, inv_tau);                            \
     else                                                                                                             \
-        launch_pdl(small_linear_thread_kernel<TX, TW>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st,      \
-                   (const TX*)x, (const TW*)w, out, N, K, total, bias, bias_dt, inv_tau);
+        launch_pdl(small_linear_thread_kernel<TX, TW>, dim3((N + SL_OUTS - 1) / SL_OUTS, (T + SL_ROWS - 1) / SL_ROWS), \
+                   dim3(SL_ROWS * SL_OUTS), 0, st, (const TX*)x, (const TW*)w, out, T, N, K, bias, bias_dt, inv_tau);
     if (x_dt == QNN_DT_BF16 && w_dt == QNN_DT_BF16) { QNN_SL(bf16, bf16) }
     else if (x_dt == QNN_DT_BF16) { QNN_SL(bf16, float) }
     else if (w_dt == QNN_DT_BF16) { QNN_SL(float, bf16) }

@@ -881,12 +881,21 @@ def small_linear_f32(x: torch.Tensor, w: torch.Tensor, decay_bias: Optional[torc
 
 # ---- gated linear attention -------------------------------------------------------------------------------
 
+GLA_SEGMENT = 256            # rows of a segment when long sequences are walked in segments side by side
+GLA_SEGMENTS_FROM = 512      # the longest sequence of a step from which that is done
+
+
 def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, q_scale: float,
              seq_row0: Optional[torch.Tensor], seq_len: Optional[torch.Tensor], slots: torch.Tensor,
-             state: torch.Tensor, n_seqs: int, n_heads: int, dim: int, vdim: int) -> torch.Tensor:
+             state: torch.Tensor, n_seqs: int, n_heads: int, dim: int, vdim: int, longest: int = 0) -> torch.Tensor:
     """The recurrence S = diag(a) S + k v^T, o = S^T (q q_scale) over the rows of every sequence in order, from the
     state of the sequence's slot and back into it.  ``proj`` holds q and k ([*, heads*dim]) and v ([*, heads*vdim])
-    from the given columns on; ``decay`` the decays a, float32 [rows, heads*dim]; returns o, float32 [rows, heads*vdim]."""
+    from the given columns on; ``decay`` the decays a, float32 [rows, heads*dim]; returns o, float32 [rows, heads*vdim].
+
+    ``longest``: the most rows that one sequence brings (0: unknown).  From 512 rows on the sequences are cut into
+    segments of 256 rows that run side by side (the recurrence is linear in the state: each segment's own state and
+    decay product first, a short pass over the segments in order, then the outputs); results differ from the walk
+    in one piece by rounding only."""
     _req(proj, "proj", None, 2)
     _req(decay, "decay", torch.float32, 2)
     _req(slots, "slots", torch.int32, 1)
@@ -901,6 +910,15 @@ def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torc
     if seq_row0 is None and T < n_seqs:
         raise ValueError("gla_scan: fewer rows than sequences")
     out = torch.empty((T, n_heads * vdim), dtype=torch.float32, device=proj.device)
+    if seq_row0 is not None and longest >= GLA_SEGMENTS_FROM and n_seqs * -(-longest // GLA_SEGMENT) <= 65535:
+        nseg = -(-longest // GLA_SEGMENT)
+        scratch = torch.zeros((n_seqs * nseg, n_heads, dim, vdim), dtype=torch.float32, device=proj.device)
+        seg_decay = torch.empty((n_seqs * nseg, n_heads * dim), dtype=torch.float32, device=proj.device)
+        _lib.check(_lib.load().qnn_gla_scan_segments(
+            _col_ptr(proj, q_col), _col_ptr(proj, k_col), _col_ptr(proj, v_col), proj.shape[1], dt_code(proj), _p(decay),
+            decay.shape[1], float(q_scale), _p(seq_row0), _p(seq_len), _p(slots), _p(state), _p(out), out.shape[1],
+            n_seqs, n_heads, dim, vdim, GLA_SEGMENT, nseg, _p(scratch), _p(seg_decay), _stream()), "gla_scan_segments", 4)
+        return out
     _lib.check(_lib.load().qnn_gla_scan(
         _col_ptr(proj, q_col), _col_ptr(proj, k_col), _col_ptr(proj, v_col), proj.shape[1], dt_code(proj), _p(decay),
         decay.shape[1], float(q_scale), _p(seq_row0), _p(seq_len), _p(slots), _p(state),

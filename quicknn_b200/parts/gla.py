@@ -80,6 +80,7 @@ class GatedLinearAttention(Mixer):
         o = ops.gla_scan(p, 0, H * d, 2 * H * d, a, float(d) ** -0.5,
                          None if step.mode == "decode" else step.seq_row0,
                          None if step.mode == "decode" else step.seq_len,
-                         step.slots, line.state, step.n_seqs, H, d, vd)
+                         step.slots, line.state, step.n_seqs, H, d, vd,
+                         longest=0 if step.mode == "decode" else step.max_q_len)
         g = ops.gla_norm_gate(o, self.norm, self.eps, p, 2 * H * d + H * vd, H, vd)
         return project(g, self.w_o)

@@ -260,6 +260,44 @@ def test_gated_linear_attention_alone_prompts_then_single_tokens_then_a_reused_s
     assert np.abs(y - ref[2][:37]).max() < 2e-5 * max(1.0, np.abs(ref[2]).max())
 
 
+def test_long_prompts_walk_their_segments_side_by_side():
+    """From 512 rows on a step's sequences are cut into segments of 256 rows: beside a long prompt a short one
+    (segments of no rows) and one that ends inside a segment; then a long portion onto a state that is not empty."""
+    from quicknn_b200.cache import KVCache
+    from quicknn_b200.kernels import ops
+    from quicknn_b200.parts import MIXERS, PartSpec
+    W, heads, dim, vdim, rank, tau = 32, 2, 24, 40, 4, 7.0
+    spec = PartSpec("gla", {"hidden_size": W, "n_heads": heads, "dim": dim, "vdim": vdim, "tau": tau, "decay_rank": rank,
+                            "eps": 1e-5})
+    mixer = MIXERS.get("gla")(spec)
+    w = {"q": rnd((heads * dim, W), 1, 0.3), "k": rnd((heads * dim, W), 2, 0.3), "v": rnd((heads * vdim, W), 3, 0.3),
+         "g": rnd((heads * vdim, W), 4, 0.3), "o": rnd((W, heads * vdim), 5, 0.3), "norm": rnd(vdim, 6, 0.2) + 1,
+         "a1": rnd((rank, W), 7, 0.3), "a2": rnd((heads * dim, rank), 8, 0.5),
+         "a2.b": np.linspace(0, 11, heads * dim).astype(np.float32)}
+    names = {"q": "q", "k": "k", "v": "v", "g": "gate", "o": "o", "norm": "norm", "a1": "a1", "a2": "a2", "a2.b": "a2_bias"}
+    mixer.load({names[k]: dev(v) for k, v in w.items()}, torch.float32, DEV)
+    cache = KVCache([None], [mixer.state_need()], 4096, 3, 2048, torch.float32, DEV)
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau}
+    w64 = {k: v.astype(np.float64) for k, v in w.items()}
+    lens = [700, 5, 300]
+    assert max(lens) >= ops.GLA_SEGMENTS_FROM
+    xs = [rnd((n + 650, W), 40 + i) for i, n in enumerate(lens)]
+    ref = [FP.gla(x.astype(np.float64), w64, m, 1e-5) for x in xs]
+    slots = [cache.allocate() for _ in lens]
+    step = part_step(lens, [0, 0, 0], slots, "prefill", torch.float32, cache, mixer)
+    y = host(mixer.forward(dev(np.concatenate([x[:n] for x, n in zip(xs, lens)])), step, cache.line(0)))
+    want = np.concatenate([r[:n] for r, n in zip(ref, lens)])
+    assert np.abs(y - want).max() < 3e-5 * max(1.0, np.abs(want).max())
+    step = part_step([600, 1], [700, 300], [slots[0], slots[2]], "extend", torch.float32, cache, mixer)
+    y = host(mixer.forward(dev(np.concatenate([xs[0][700:1300], xs[2][300:301]])), step, cache.line(0)))
+    want = np.concatenate([ref[0][700:1300], ref[2][300:301]])
+    assert np.abs(y - want).max() < 3e-5 * max(1.0, np.abs(want).max())
+    step = part_step([1, 1], [1300, 301], [slots[0], slots[2]], "decode", torch.float32, cache, mixer)
+    y = host(mixer.forward(dev(np.stack([xs[0][1300], xs[2][301]])), step, cache.line(0)))
+    want = np.stack([ref[0][1300], ref[2][301]])
+    assert np.abs(y - want).max() < 3e-5 * max(1.0, np.abs(want).max())
+
+
 @pytest.mark.parametrize("dtype,kv_rank,window", [(torch.float32, 48, 7), (torch.float32, 64, 64), (torch.float32, 32, 65),
                                                   (torch.float32, 24, None), (torch.bfloat16, 64, 9),
                                                   (torch.bfloat16, 128, 64), (torch.bfloat16, 256, 65)])
