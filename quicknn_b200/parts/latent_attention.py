@@ -42,10 +42,13 @@ class LatentAttentionMixer(AttentionMixer):
         self.q_rank = int(p["q_rank"])
         self.kv_rank = int(p["kv_rank"])
         self.eps = float(p["eps"])
+        # the attention kernels take head sizes in whole 16-byte pieces: a latent of another size is carried with
+        # zero columns behind it (they add nothing to a score and meet zero columns of the output matrix)
+        self.rank_pad = (self.kv_rank + 7) // 8 * 8
         inner = PartSpec("attention", {
-            "hidden_size": self.hidden, "n_heads": self.n_heads, "n_kv_heads": 1, "head_dim": self.kv_rank,
+            "hidden_size": self.hidden, "n_heads": self.n_heads, "n_kv_heads": 1, "head_dim": self.rank_pad,
             "scale": float(p["scale"]), "softcap": None, "window": p.get("window"),
-            "position": PartSpec("none", {"head_dim": self.kv_rank})})
+            "position": PartSpec("none", {"head_dim": self.rank_pad})})
         super().__init__(inner)
         self.spec = spec
         self.w_in: Optional[torch.Tensor] = None        # [q_rank + kv_rank, width]: W_dq over W_dkv
@@ -77,45 +80,51 @@ class LatentAttentionMixer(AttentionMixer):
         uv = tensors["uv"].to(wide).view(H, vd, r)
         wo = tensors["o"].to(wide).view(self.hidden, H, vd)
         keep = tensors["uq"].dtype
-        self.w_qk = torch.einsum("hdr,hdq->hrq", uk, uq).reshape(H * r, self.q_rank).to(keep).contiguous()
-        self.w_ov = torch.einsum("whv,hvr->whr", wo, uv).reshape(self.hidden, H * r).to(keep).contiguous()
+        rp = self.rank_pad
+        w_qk = torch.zeros((H, rp, self.q_rank), dtype=wide, device=uq.device)
+        w_qk[:, :r] = torch.einsum("hdr,hdq->hrq", uk, uq)
+        w_ov = torch.zeros((self.hidden, H, rp), dtype=wide, device=uq.device)
+        w_ov[:, :, :r] = torch.einsum("whv,hvr->whr", wo, uv)
+        self.w_qk = w_qk.reshape(H * rp, self.q_rank).to(keep).contiguous()
+        self.w_ov = w_ov.reshape(self.hidden, H * rp).to(keep).contiguous()
         self.position.prepare(device)
-        why = (ops.attention_refusal(compute_dtype, H, 1, r) or ops.linear_refusal(self.w_in.dtype, self.hidden))
+        why = (ops.attention_refusal(compute_dtype, H, 1, rp) or ops.linear_refusal(self.w_in.dtype, self.hidden))
         if why:
             raise ValueError(f"latent attention mixer: {why}")
         dev = torch.device(device)
         sms = torch.cuda.get_device_properties(dev).multi_processor_count if dev.type == "cuda" else 148
-        self._resident = sms * max(1, min(8, 512 // max(1, r)))
+        self._resident = sms * max(1, min(8, 512 // max(1, rp)))
 
     def weight_bytes(self) -> int:
         ws = (self.w_in, self.w_gate, self.w_qk, self.w_ov, self.norm_q, self.norm_kv)
         return sum(w.numel() * w.element_size() for w in ws)
 
     def cache_need(self) -> Optional[CacheNeed]:
-        return CacheNeed(1, self.kv_rank, self.window, values=False)
+        return CacheNeed(1, self.rank_pad, self.window, values=False)
 
     def forward(self, x: torch.Tensor, step, line) -> torch.Tensor:
-        H, r, rq = self.n_heads, self.kv_rank, self.q_rank
+        H, r, rq, rp = self.n_heads, self.kv_rank, self.q_rank, self.rank_pad
         T = x.shape[0]
+        new = torch.empty if rp == r else torch.zeros              # columns behind the latent stay zero
         a = project(x, self.w_in)                                           # [T, q_rank + kv_rank]
         gate = ops.small_linear_f32(x, self.w_gate)                         # [T, heads], float32
         cq = torch.empty((T, rq), dtype=a.dtype, device=a.device)
         ops.rmsnorm_cols(a, 0, rq, self.norm_q, self.eps, cq)
-        q = project(cq, self.w_qk)                                          # [T, heads * kv_rank]: queries on the latent's side
+        q = project(cq, self.w_qk)                                          # [T, heads * rank]: queries on the latent's side
         if step.mode == "decode":
             # the query rows serve as they are; the latent goes to the cache line and is read from there
             if line.writes:
-                kv = torch.empty((T, 2 * r), dtype=a.dtype, device=a.device)      # k | (no v): the append's row layout
+                kv = new((T, 2 * rp), dtype=a.dtype, device=a.device)             # k | (no v): the append's row layout
                 ops.rmsnorm_cols(a, rq, r, self.norm_kv, self.eps, kv)
-                ops.cache_append(kv, 0, 1, r, step.tok_pos, step.tok_slot, line)
+                ops.cache_append(kv, 0, 1, rp, step.tok_pos, step.tok_slot, line)
             o = self.attend(q, step, line)
         else:
             # packed rows q | c | c: the latent is key and value of the one shared head
-            packed = torch.empty((T, (H + 2) * r), dtype=a.dtype, device=a.device)
+            packed = new((T, (H + 2) * rp), dtype=a.dtype, device=a.device)
             ops.copy_cols(q, packed, 0)
-            ops.rmsnorm_cols(a, rq, r, self.norm_kv, self.eps, packed, H * r, (H + 1) * r)
+            ops.rmsnorm_cols(a, rq, r, self.norm_kv, self.eps, packed, H * rp, (H + 1) * rp)
             if step.mode == "prefill" and line.writes:
-                ops.cache_append(packed, H, 1, r, step.tok_pos, step.tok_slot, line)
+                ops.cache_append(packed, H, 1, rp, step.tok_pos, step.tok_slot, line)
             o = self.attend(packed, step, line)
         ops.scale_heads(o, gate, H)
         return project(o, self.w_ov)

@@ -10,13 +10,22 @@ from typing import Dict, List
 import numpy as np
 
 
+def cache_tokens(max_tokens: int) -> int:
+    """Tokens to size the cache for: every live request may waste up to a page less one token, and there are at most
+    as many live requests as tokens (and never more than the engine has slots)."""
+    from .cache import PAGE
+    pages = (max(1, max_tokens) + PAGE - 1) // PAGE
+    return (pages + min(max(1, max_tokens), 256)) * PAGE
+
+
 def main(argv: List[str]) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description="replay token traces and write logits")
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", required=True, type=int,
-                    help="most tokens that live requests hold at any time (each rounded up to 64)")
+                    help="most tokens that live requests hold at any time; what the cache adds by rounding every "
+                         "request up to whole pages is not counted, so a page per possible request is added")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -28,7 +37,7 @@ def main(argv: List[str]) -> int:
         return 3
     os.makedirs(args.out, exist_ok=True)
     model = Model.from_folder(args.model, args.dtype, args.device)
-    engine = Engine(model, max_tokens=args.max_tokens)
+    engine = Engine(model, max_tokens=cache_tokens(args.max_tokens))
     slots: Dict[str, int] = {}
 
     for line in sys.stdin:
