@@ -3,7 +3,7 @@
 //   qnn_moe_route      router logits (float32 sums), a score function, the `top` best experts of every row
 //                      (ties to the lower index) and their scores
 //   qnn_moe_plan       rows grouped by expert: offsets, a permutation, and a list of (expert, first row) tiles of
-//                      up to 16 rows; one block
+//                      up to 16, 64 or 128 rows; one block
 //   qnn_moe_gate_up    per tile: gathered rows (times their score, when the score goes on the input) against the
 //                      expert's stacked gate|up matrix, then the gated activation
 //   qnn_moe_down       per tile: the expert's down matrix; rows go back to where they came from (float32),
@@ -465,7 +465,8 @@ QNN_API int qnn_moe_max_tiles(int n_entries, int E, int tile_rows) { return (n_e
 QNN_API int qnn_moe_plan(const int* sel_e, int n, int E, int tile_rows, int* offsets, int* perm, int* tiles, int* n_tiles,
                          cudaStream_t st) {
     if (n <= 0) return 0;
-    if (E <= 0 || (size_t)2 * E * sizeof(int) > 48 * 1024 || (tile_rows != 16 && tile_rows != 64)) return QNN_ERR_ARGUMENT;
+    if (E <= 0 || (size_t)2 * E * sizeof(int) > 48 * 1024 || (tile_rows != 16 && tile_rows != 64 && tile_rows != 128))
+        return QNN_ERR_ARGUMENT;
     launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), st, sel_e, n, E, tile_rows, offsets, perm,
                tiles, n_tiles);
     QNN_LAUNCH_CHECK();

@@ -80,6 +80,9 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_moe_gate_up": [c_vp, c_int, c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int,
                         c_float, c_float, c_vp, c_vp],
     "qnn_moe_down": [c_vp, c_int, c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp],
+    "qnn_moe_gather": [c_vp, c_int, c_vp, c_vp, c_int, c_int, c_vp, c_int, c_vp],
+    "qnn_moe_tcgen05": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int,
+                        c_float, c_float, c_vp, c_vp],
     "qnn_moe_combine": [c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_vp],
     "qnn_gated_act_clamped": [c_vp, c_vp, c_int, c_int, c_int, c_float, c_float, c_vp],
 }

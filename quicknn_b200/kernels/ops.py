@@ -966,12 +966,20 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, score: str = "s
     return sel_e, sel_w
 
 
+MOE_GROUPED_FROM = 64        # rows per expert (on average) from which prompts take the grouped tcgen05 product
+
+
 def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: int, w_gate_up: torch.Tensor,
                 w_down: torch.Tensor, activation: int, limit: float, alpha: float, weight_on_input: bool,
-                shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+                shared: Optional[torch.Tensor] = None, grouped: Optional[bool] = None) -> torch.Tensor:
     """sum over a row's chosen experts of down_e(act(gate_e(x'), up_e(x'))) (+ ``shared``), float32 [rows, width].
     The score multiplies the expert's input (x' = score * x) or its output.  w_gate_up: [experts, 2*ff, width]
-    (gate rows, then up rows); w_down: [experts, width, ff].  Everything stays on the device."""
+    (gate rows, then up rows); w_down: [experts, width, ff].  Everything stays on the device.
+
+    Three kinds of tile: with many rows per expert (prompts; bfloat16, the clamped activation, widths in whole 16-byte
+    pieces) the rows are gathered expert after expert and both products are grouped tcgen05 GEMMs over tiles of 128
+    rows (``grouped``: None = by size); else tensor-core tiles of 16 or 64 rows (mma.sync) where the widths are whole
+    blocks of 32; else plain tiles."""
     _req(x, "x", None, 2)
     _req(w_gate_up, "w_gate_up", x.dtype, 3)
     _req(w_down, "w_down", x.dtype, 3)
@@ -982,7 +990,11 @@ def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: 
         raise ValueError("moe_experts: shapes do not agree")
     L = _lib.load()
     n = T * top
-    tile_rows = int(L.qnn_moe_tile_rows(n, E, dt_code(x), W, ff))       # 16, or 64 where experts get many rows each
+    if grouped is None:
+        grouped = n >= MOE_GROUPED_FROM * E
+    grouped = bool(grouped and USE_TCGEN05 and x.dtype == torch.bfloat16 and activation == GATED_CLAMPED
+                   and W % 8 == 0 and ff % 8 == 0)
+    tile_rows = 128 if grouped else int(L.qnn_moe_tile_rows(n, E, dt_code(x), W, ff))   # else 16, or 64 with many rows each
     max_tiles = int(L.qnn_moe_max_tiles(n, E, tile_rows))
     meta = torch.empty(E + 1 + n + 2 * max_tiles + 1, dtype=torch.int32, device=x.device)
     offsets, perm = meta[:E + 1], meta[E + 1:E + 1 + n]
@@ -990,19 +1002,40 @@ def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: 
     _lib.check(L.qnn_moe_plan(_p(sel_e), n, E, tile_rows, _p(offsets), _p(perm), _p(tiles), _p(n_tiles), _stream()),
                "moe_plan")
     hidden = torch.empty((n, ff), dtype=x.dtype, device=x.device)
+    ys = torch.empty((n, W), dtype=torch.float32, device=x.device)
+    if grouped:
+        gathered = torch.empty((n, W), dtype=x.dtype, device=x.device)
+        status = _p(_status_word(x.device))
+        _lib.check(L.qnn_moe_gather(_p(x), W, _p(perm), _p(sel_w), top, int(weight_on_input), _p(gathered), n, _stream()),
+                   "moe_gather")
+        code = L.qnn_moe_tcgen05(_p(gathered), _p(w_gate_up), _p(hidden), n, E, 2 * ff, W, EPI_GATED, _p(offsets), _p(perm),
+                                 _p(sel_w), _p(tiles), _p(n_tiles), max_tiles, 0, float(limit), float(alpha), status,
+                                 _stream())
+        if code == _lib.ERR_UNSUPPORTED:           # sizes the grouped product refuses: the other tiles
+            return moe_experts(x, sel_e, sel_w, top, w_gate_up, w_down, activation, limit, alpha, weight_on_input, shared,
+                               grouped=False)
+        _lib.check(code, "moe_tcgen05")
+        _lib.check(L.qnn_moe_tcgen05(_p(hidden), _p(w_down), _p(ys), n, E, W, ff, EPI_NONE, _p(offsets), _p(perm), _p(sel_w),
+                                     _p(tiles), _p(n_tiles), max_tiles, int(not weight_on_input), 0.0, 0.0, status,
+                                     _stream()), "moe_tcgen05")
+        return _moe_sum(L, ys, top, shared, T, W)
     _lib.check(L.qnn_moe_gate_up(_p(x), dt_code(x), W, _p(w_gate_up), ff, _p(offsets), _p(perm), _p(sel_w), _p(tiles),
                                  _p(n_tiles), max_tiles, tile_rows, top, int(weight_on_input), int(activation), float(limit),
                                  float(alpha), _p(hidden), _stream()), "moe_gate_up")
-    ys = torch.empty((n, W), dtype=torch.float32, device=x.device)
     _lib.check(L.qnn_moe_down(_p(hidden), dt_code(x), ff, _p(w_down), W, _p(offsets), _p(perm), _p(sel_w), _p(tiles),
                               _p(n_tiles), max_tiles, tile_rows, int(not weight_on_input), _p(ys), _stream()), "moe_down")
+    return _moe_sum(L, ys, top, shared, T, W)
+
+
+def _moe_sum(L, ys: torch.Tensor, top: int, shared: Optional[torch.Tensor], T: int, W: int) -> torch.Tensor:
+    """out[t] = sum over the row's experts (+ the shared expert's output), float32."""
     if top == 1 and shared is None:
         return ys
     if shared is not None:
         _req(shared, "shared", None, 2)
         if tuple(shared.shape) != (T, W):
             raise ValueError("moe_experts: the shared expert's output has another shape")
-    out = torch.empty((T, W), dtype=torch.float32, device=x.device)
+    out = torch.empty((T, W), dtype=torch.float32, device=ys.device)
     _lib.check(L.qnn_moe_combine(_p(ys), top, _p(shared), dt_code(shared) if shared is not None else 0, _p(out), T, W,
                                  _stream()), "moe_combine")
     return out

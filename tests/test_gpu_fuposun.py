@@ -389,6 +389,18 @@ def test_routed_experts_alone(dtype, experts, top, shared, W, ff):
         got = host(part.forward(dev(x, dtype), None))
         ref = FP.routed_ff(x.astype(np.float64), w64, mlp)
         assert np.abs(got - ref).max() < (2e-5 if dtype == torch.float32 else 3e-2) * max(1.0, np.abs(ref).max())
+    if dtype == torch.bfloat16:
+        # the three kinds of tile give the same sums: grouped tcgen05 tiles of 128 rows against mma.sync tiles of
+        # 64 and 16 rows (or the plain tiles where the widths are no whole blocks of 32)
+        from quicknn_b200.kernels import ops
+        xb = dev(bf(rnd((700, W), 900)), dtype)
+        sel_e, sel_w = ops.moe_route(xb, part.w_router, top)
+        outs = [host(ops.moe_experts(xb, sel_e, sel_w, top, part.w_gate_up, part.w_down, ops.GATED_CLAMPED, limit, 1.702,
+                                     True, None, grouped=g)) for g in (True, False)]
+        few = host(ops.moe_experts(xb[:40].contiguous(), sel_e[:40 * top].contiguous(), sel_w[:40 * top].contiguous(), top,
+                                   part.w_gate_up, part.w_down, ops.GATED_CLAMPED, limit, 1.702, True, None, grouped=False))
+        scale = max(1.0, np.abs(outs[1]).max())
+        assert np.abs(outs[0] - outs[1]).max() < 2e-2 * scale and np.abs(few - outs[1][:40]).max() < 2e-2 * scale
     # a row's result does not depend on the rows beside it
     x = bf(rnd((150, W), 350))
     alone = host(part.forward(dev(x[77:78], dtype), None))
