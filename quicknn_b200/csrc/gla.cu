@@ -75,24 +75,27 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
             const int i = part * RPT + r;
             S[r][c] = (slot >= 0 && i < dim && col + c < vdim) ? my_state[(size_t)i * vdim + c] : 0.f;
         }
-    float rq[C::PER_THREAD], rk[C::PER_THREAD], ra[C::PER_THREAD], rv[C::V_PER_THREAD];
+    // what is loaded stays as it came until `put`: a conversion here would wait for the load at once, and the loads
+    // are meant to be in flight while the rows before them are walked
+    T rq[C::PER_THREAD], rk[C::PER_THREAD], rv[C::V_PER_THREAD];
+    float ra[C::PER_THREAD];
     auto fetch = [&](int t0) {                               // global memory -> registers (rows beyond the sequence: nothing)
         const int nt = min(GLA_ROWS, n - t0);
 #pragma unroll
         for (int e = 0; e < C::PER_THREAD; ++e) {
             const int idx = threadIdx.x + e * GLA_THREADS, tt = idx / DIMP, i = idx - tt * DIMP;
-            rq[e] = 0.f; rk[e] = 0.f; ra[e] = 1.f;
+            rq[e] = from_f<T>(0.f); rk[e] = from_f<T>(0.f); ra[e] = 1.f;
             if (tt < nt && i < dim) {
                 const size_t row = (size_t)(row0 + t0 + tt);
-                rq[e] = to_f(q[row * ld + h * dim + i]) * q_scale;
-                rk[e] = to_f(k[row * ld + h * dim + i]);
+                rq[e] = q[row * ld + h * dim + i];
+                rk[e] = k[row * ld + h * dim + i];
                 ra[e] = decay[row * ldd + h * dim + i];
             }
         }
 #pragma unroll
         for (int e = 0; e < C::V_PER_THREAD; ++e) {
             const int idx = threadIdx.x + e * GLA_THREADS, tt = idx / C::COLS, c = idx - tt * C::COLS;
-            rv[e] = (tt < nt && c0 + c < vdim) ? to_f(v[(size_t)(row0 + t0 + tt) * ld + h * vdim + c0 + c]) : 0.f;
+            rv[e] = (tt < nt && c0 + c < vdim) ? v[(size_t)(row0 + t0 + tt) * ld + h * vdim + c0 + c] : from_f<T>(0.f);
         }
     };
     auto put = [&](float* buf) {                             // registers -> shared memory
@@ -100,12 +103,12 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
         for (int e = 0; e < C::PER_THREAD; ++e) {
             const int idx = threadIdx.x + e * GLA_THREADS, tt = idx / DIMP, i = idx - tt * DIMP;
             const int at = tt * C::ROW + (i / RPT) * C::PART + (i % RPT);
-            buf[at] = rq[e];
-            buf[C::ARRAY + at] = rk[e];
+            buf[at] = to_f(rq[e]) * q_scale;
+            buf[C::ARRAY + at] = to_f(rk[e]);
             buf[2 * C::ARRAY + at] = ra[e];
         }
 #pragma unroll
-        for (int e = 0; e < C::V_PER_THREAD; ++e) buf[3 * C::ARRAY + threadIdx.x + e * GLA_THREADS] = rv[e];
+        for (int e = 0; e < C::V_PER_THREAD; ++e) buf[3 * C::ARRAY + threadIdx.x + e * GLA_THREADS] = to_f(rv[e]);
     };
     fetch(0);
     put(sm);
