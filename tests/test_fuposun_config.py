@@ -130,3 +130,16 @@ def test_plain_mechanisms_against_other_ways_of_writing_them():
     gate = np.array([[3.0, -3.0]])
     assert np.allclose(FP.clamped_expert(np.eye(1), gate.T, np.array([[5.0], [-5.0]]), np.eye(2), 1.0),
                        [[1 / (1 + np.exp(-1.702)) * 2.0, 0.0]])
+
+
+def test_the_command_line_writes_and_describes_a_random_model(tmp_path, capsys):
+    from quicknn_b200.cli import main
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(RAW))
+    out = tmp_path / "model"
+    assert main(["random", "--config", str(cfg), "--seed", "3", "--out", str(out)]) == 0
+    capsys.readouterr()
+    assert main(["info", "--model", str(out)]) == 0
+    info = json.loads(capsys.readouterr().out)
+    assert info["architecture"] == "Fuposun" and info["layers"] == 3
+    assert info["config"]["layers"][0]["mixer"]["decay_rank"] == 3 and info["config"]["layers"][0]["mlp"] is None

@@ -119,6 +119,9 @@ def make_folder(base, name, storage, peaky, keep_rank=True):
                 tensors[f"l{i}.mlp.router"] = r
                 tensors[f"l{i}.norm2"][:most] = 1.0            # equal weights keep the ranking's spacing
         tensors["embed.norm"][:most] = 1.0
+        for k in list(tensors):                            # and no layer writes into the ranking's columns
+            if k.endswith((".mix.o", ".down")):
+                tensors[k][:most] = 0.0
     dt = torch.float32 if storage == "float32" else torch.bfloat16
     out = cfg.to_dict()
     if not keep_rank:                      # as a file from elsewhere: the decay's rank is the tensor's extent
@@ -500,3 +503,68 @@ def test_long_decoding_keeps_state_and_window(fupo):
     for i, t in enumerate(got):                 # every generated token is the best one at its place
         row = ref[len(p) - 1 + i]
         assert row[t] >= row.max() - 1e-4 * max(1.0, np.abs(row).max()), f"token {i}"
+
+
+# ---- configurations drawn at random ---------------------------------------------------------------------------------
+
+def random_config(seed):
+    """Every size, the order of the layers and every constant drawn from a seed."""
+    rng = np.random.default_rng(1000 + seed)
+    pick = lambda xs: xs[int(rng.integers(len(xs)))]  # noqa: E731
+    width = pick([48, 64, 96, 100, 160, 320])
+    layers = []
+    for _ in range(int(rng.integers(1, 6))):
+        kind = pick(["none", "dense", "moe", "moe"])
+        if kind == "none":
+            mlp = None
+        elif kind == "dense":
+            mlp = {"kind": "dense", "ff": pick([32, 72, 128, 256])}
+        else:
+            experts = int(rng.integers(2, 17))
+            mlp = _moe(experts, int(rng.integers(1, min(4, experts) + 1)), pick([16, 40, 64, 96]), pick([0.3, 1.0, 7.0]),
+                       pick([None, (pick([24, 32, 96]), pick([0.5, 1.5]))]))
+        if rng.random() < 0.6:
+            layers.append(_latent(int(rng.integers(1, 9)), pick([8, 16, 24, 32, 64]), pick([8, 16, 32, 48]),
+                                  pick([16, 24, 64, 128]), pick([16, 32, 40, 64, 96, 128, 256]),
+                                  float(rng.uniform(0.1, 0.5)), pick([None, 1, 3, 17, 63, 64, 65, 72, 100]), mlp))
+        else:
+            layers.append(_gla(int(rng.integers(1, 7)), pick([4, 8, 16, 32, 64, 128]), pick([8, 16, 32, 64]),
+                               float(rng.uniform(2.0, 32.0)), pick([4, 8, 16, 32]), mlp))
+    return dict(architecture="Fuposun", vocab=int(rng.integers(100, 700)), width=width,
+                residual_mult=float(pick([1.0, 0.7, 0.35])), logit_softcap=pick([None, 12.0, 30.0]),
+                norm={"eps": pick([1e-5, 1e-6])}, initializer_range=0.07, layers=layers)
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Prompts of unequal lengths in one step, then tokens one by one, against the plain logits: float32 sharply for
+    every configuration, bfloat16 for every other one.  (A wider sweep of 100 seeds passed but for two bfloat16 cases,
+    both at the first token of a sequence in a linear-attention layer: there the state has rank one, o = v (k . q),
+    and the norm that follows keeps only the sign of k . q, which rounding can turn when the product is near zero;
+    float32 agrees there too.)"""
+    from quicknn_b200.engine import Engine, Model
+    raw = random_config(seed)
+    name = f"R{seed}"
+    CONFIGS[name] = (raw, 50 + seed)
+    lens, extra = [130, 7, 1, 70], 5
+    reqs = prompts(name, [n + extra for n in lens], seed=seed)
+    for dtype in (("float32", "bfloat16") if seed % 2 == 0 else ("float32",)):
+        folder = make_folder(tmp_path, name, dtype, dtype == "float32", keep_rank=bool(seed % 3))
+        plain = FP.PlainFuposun(folder)
+        ref = [plain.logits(t) for t in reqs]
+        eng = Engine(Model.from_folder(folder, dtype, DEV), max_tokens=1024)
+        slots = [eng.new_sequence() for _ in reqs]
+        got = eng.step([(s, t[:n]) for s, t, n in zip(slots, reqs, lens)], "all").cpu().numpy()
+        at = 0
+        for r, n in zip(ref, lens):
+            ok, err, tol = close(got[at:at + n], r[:n], dtype)
+            assert ok, f"seed {seed} {dtype}: prompt of {n}: error {err:.3g} > {tol:.3g}  ({raw['layers']})"
+            at += n
+        for t in range(extra):
+            got = eng.step([(s, [q[n + t]]) for s, q, n in zip(slots, reqs, lens)], "last").cpu().numpy()
+            for i, (r, n) in enumerate(zip(ref, lens)):
+                ok, err, tol = close(got[i:i + 1], r[n + t:n + t + 1], dtype)
+                assert ok, f"seed {seed} {dtype}: request {i} decoded token {t}: error {err:.3g} > {tol:.3g}"
+        for s in slots:
+            eng.release(s)
+        eng.cache.audit()
