@@ -270,13 +270,13 @@ def design_sizes(name):
     rank, qr, d = (256, 768, 128) if name == "2b" else (128, 512, 64)
     H = W // d // 2                                            # latent heads: heads * vdim = width / 2 ... width
     latent = {"heads": 2 * H // 2, "dim": d, "vdim": d, "q_rank": qr, "kv_rank": rank, "scale": d ** -0.5, "mask": {"size": window}}
-    gla = {"heads": W // (2 * d), "dim": d, "vdim": 2 * d, "tau": 16.0, "decay_rank": 64}
+    gla = {"heads": W // (2 * d), "dim": d, "vdim": 2 * d, "tau": 8.0, "decay_rank": 64}
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": ff // 4, "limit": 7.0},
            "shared": {"ff": ff // 4, "limit": 7.0}}
     pattern = [("latent_attention", latent, dense), ("latent_attention", latent, moe), ("gla", gla, dense),
                ("latent_attention", latent, moe)]
-    fupo = dict(architecture="Fuposun", vocab=vocab, width=W, residual_mult=0.7, logit_softcap=30.0, norm={"eps": 1e-5},
+    fupo = dict(architecture="Fuposun", vocab=vocab, width=W, residual_mult=0.5, logit_softcap=50.0, norm={"eps": 1e-6},
                 layers=[{"type": t, "mixer": m, "mlp": f} for t, m, f in (pattern * layers)[:layers]])
     gemma = dict(SIZES, hidden_size=W, intermediate_size=ff, num_attention_heads=heads, num_key_value_heads=kvh,
                  head_dim=hd, num_hidden_layers=layers, vocab_size=vocab, sliding_window=window,

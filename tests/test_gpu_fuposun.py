@@ -76,7 +76,7 @@ FUPO_B = dict(architecture="Fuposun", vocab=512, width=128, residual_mult=1.0, l
                   _gla(2, 64, 32, 16.0, 16, {"kind": "dense", "ff": 192}),
                   _latent(1, 16, 32, 32, 256, 0.25, 130, {"kind": "dense", "ff": 64})])
 # C: a width, ranks and head sizes that are no multiple of 8 or of 32
-FUPO_C = dict(architecture="Fuposun", vocab=301, width=100, residual_mult=0.7, logit_softcap=15.0, norm={"eps": 1e-4},
+FUPO_C = dict(architecture="Fuposun", vocab=301, width=100, residual_mult=0.6, logit_softcap=15.0, norm={"eps": 1e-4},
               initializer_range=0.07, layers=[
                   _latent(5, 12, 20, 20, 48, 0.3, 11, {"kind": "dense", "ff": 70}),
                   _gla(3, 12, 20, 6.0, 5, _moe(4, 3, 28, 0.4, (36, 0.6)))])
@@ -304,7 +304,7 @@ def test_long_prompts_walk_their_segments_side_by_side():
 @pytest.mark.parametrize("dtype,kv_rank,window,H", [
     (torch.float32, 48, 7, 3), (torch.float32, 64, 64, 3), (torch.float32, 32, 65, 3), (torch.float32, 24, None, 3),
     (torch.bfloat16, 64, 9, 3), (torch.bfloat16, 128, 64, 3), (torch.bfloat16, 256, 65, 3),
-    (torch.float32, 128, 72, 8), (torch.bfloat16, 128, 72, 8), (torch.bfloat16, 64, 1, 16),      # many heads on the one latent
+    (torch.float32, 128, 80, 8), (torch.bfloat16, 128, 80, 8), (torch.bfloat16, 64, 1, 16),      # many heads on the one latent
     (torch.float32, 20, 6, 2), (torch.bfloat16, 20, 6, 2), (torch.bfloat16, 100, 40, 5)])      # ranks that are no multiple of 8
 def test_latent_attention_alone_and_a_window_one_token_off_would_show(dtype, kv_rank, window, H):
     from quicknn_b200.cache import KVCache
@@ -358,10 +358,10 @@ def test_latent_attention_alone_and_a_window_one_token_off_would_show(dtype, kv_
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,top,shared", [(5, 1, None), (6, 2, (24, 1.1)), (3, 3, None), (40, 4, (8, 0.4))])
-@pytest.mark.parametrize("W,ff", [(72, 40), (128, 64), (320, 96)])
+@pytest.mark.parametrize("W,ff", [(72, 40), (128, 64), (352, 160)])
 def test_routed_experts_alone(dtype, experts, top, shared, W, ff):
     """Widths in whole blocks of 32 take the tensor-core tiles in bfloat16 (16 rows, and 64 where the experts get many
-    rows each), other widths and float32 the plain tiles; (320, 96): more than one block of inner elements."""
+    rows each), other widths and float32 the plain tiles; (352, 160): more than one block of inner elements."""
     from quicknn_b200.parts import FEED_FORWARDS, PartSpec
     limit = 0.35
     sh = None if shared is None else PartSpec("clamped_mlp", {"hidden_size": W, "intermediate_size": shared[0],
@@ -511,7 +511,7 @@ def random_config(seed):
     """Every size, the order of the layers and every constant drawn from a seed."""
     rng = np.random.default_rng(1000 + seed)
     pick = lambda xs: xs[int(rng.integers(len(xs)))]  # noqa: E731
-    width = pick([48, 64, 96, 100, 160, 320])
+    width = pick([48, 64, 96, 100, 160, 352])
     layers = []
     for _ in range(int(rng.integers(1, 6))):
         kind = pick(["none", "dense", "moe", "moe"])
@@ -526,7 +526,7 @@ def random_config(seed):
         if rng.random() < 0.6:
             layers.append(_latent(int(rng.integers(1, 9)), pick([8, 16, 24, 32, 64]), pick([8, 16, 32, 48]),
                                   pick([16, 24, 64, 128]), pick([16, 32, 40, 64, 96, 128, 256]),
-                                  float(rng.uniform(0.1, 0.5)), pick([None, 1, 3, 17, 63, 64, 65, 72, 100]), mlp))
+                                  float(rng.uniform(0.1, 0.5)), pick([None, 1, 3, 17, 63, 64, 65, 80, 100]), mlp))
         else:
             layers.append(_gla(int(rng.integers(1, 7)), pick([4, 8, 16, 32, 64, 128]), pick([8, 16, 32, 64]),
                                float(rng.uniform(2.0, 32.0)), pick([4, 8, 16, 32]), mlp))
