@@ -7,6 +7,7 @@
 //                            two places with a row pitch of their own (a piece of a stacked
 //                            product's output normed into a packed buffer)
 //   qnn_scale_heads          x[t, h, :] *= sigmoid(gate[t, h]): a gate per head, float32 math
+//   qnn_gate_heads           the same with the gate's logits x . w_h formed in the kernel
 //   qnn_small_linear_f32     x w^T with float32 sums and float32 results, for the few outputs that feed
 //                            float32 math (gates, decay logits)
 #include "common.cuh"
@@ -122,6 +123,42 @@ small_linear_thread_kernel(const TX* __restrict__ x, const TW* __restrict__ w, f
     out[(size_t)(t0 + r) * N + n0 + c] = finish(d, bias, bias_dt, inv_tau, n0 + c);
 }
 
+// o[t, h, :] *= sigmoid(x[t, :] . w[h, :]): the gate per head formed (float32) and applied in one kernel; a block per
+// row, the warps share the heads.  A lane's terms and the order of their sum depend on the width only.
+template <typename TX, typename TW>
+__global__ void gate_heads_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int W, void* __restrict__ o, int o_dt,
+                                  int H, int D) {
+    extern __shared__ float gate[];                       // [H]
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    const TX* xr = x + (size_t)blockIdx.x * W;
+    constexpr int VX = Vec16<TX>::N, VW = Vec16<TW>::N, V = VX > VW ? VX : VW;
+    const bool vec = (W % V) == 0 && ((((uintptr_t)x | (uintptr_t)w) & 15) == 0);
+    for (int h = warp; h < H; h += nwarp) {
+        const TW* wr = w + (size_t)h * W;
+        float d = 0.f;
+        if (vec) {                                          // 16-byte loads where the rows allow
+            for (int i = lane * V; i < W; i += 32 * V) {
+                float xf[V], wf[V];
+#pragma unroll
+                for (int j = 0; j < V; j += VX) { Vec16<TX> v; v.load(xr + i + j); v.unpack(xf + j); }
+#pragma unroll
+                for (int j = 0; j < V; j += VW) { Vec16<TW> v; v.load(wr + i + j); v.unpack(wf + j); }
+#pragma unroll
+                for (int j = 0; j < V; ++j) d += xf[j] * wf[j];
+            }
+        } else {
+            for (int i = lane; i < W; i += 32) d += to_f(xr[i]) * to_f(wr[i]);
+        }
+        d = warp_sum(d);
+        if (lane == 0) gate[h] = 1.f / (1.f + expf(-d));
+    }
+    __syncthreads();
+    const size_t base = (size_t)blockIdx.x * H * D;
+    for (int i = threadIdx.x; i < H * D; i += blockDim.x)
+        store_from_f(o, o_dt, base + i, load_as_f(o, o_dt, base + i) * gate[i / D]);
+}
+
 inline int row_threads(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
 
 }  // namespace
@@ -178,5 +215,20 @@ QNN_API int qnn_small_linear_f32(const void* x, int x_dt, const void* w, int w_d
     else if (w_dt == QNN_DT_BF16) { QNN_SL(float, bf16) }
     else { QNN_SL(float, float) }
 #undef QNN_SL
+    QNN_LAUNCH_CHECK();
+}
+
+QNN_API int qnn_gate_heads(const void* x, int x_dt, const void* w, int w_dt, int W, void* o, int o_dt, int T, int H, int D,
+                           cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (W <= 0 || H <= 0 || D <= 0 || (size_t)H * sizeof(float) > 48 * 1024) return QNN_ERR_ARGUMENT;
+    const dim3 grid(T), block(row_threads(H * D));
+    const size_t smem = (size_t)H * sizeof(float);
+#define QNN_GH(TX, TW) launch_pdl(gate_heads_kernel<TX, TW>, grid, block, smem, st, (const TX*)x, (const TW*)w, W, o, o_dt, H, D)
+    if (x_dt == QNN_DT_BF16 && w_dt == QNN_DT_BF16) QNN_GH(bf16, bf16);
+    else if (x_dt == QNN_DT_BF16) QNN_GH(bf16, float);
+    else if (w_dt == QNN_DT_BF16) QNN_GH(float, bf16);
+    else QNN_GH(float, float);
+#undef QNN_GH
     QNN_LAUNCH_CHECK();
 }

@@ -67,6 +67,7 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_rmsnorm_strided": [c_vp, c_int, c_ll, c_vp, c_int, c_float, c_vp, c_int, c_ll, c_vp, c_ll, c_int, c_int, c_vp],
     "qnn_copy_rows": [c_vp, c_int, c_ll, c_vp, c_ll, c_int, c_int, c_vp],
     "qnn_scale_heads": [c_vp, c_int, c_vp, c_int, c_int, c_int, c_vp],
+    "qnn_gate_heads": [c_vp, c_int, c_vp, c_int, c_int, c_vp, c_int, c_int, c_int, c_int, c_vp],
     "qnn_small_linear_f32": [c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_int, c_vp, c_int, c_float, c_vp],
     "qnn_gla_scan": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_float, c_vp, c_vp, c_vp, c_vp,
                      c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp],

@@ -857,6 +857,20 @@ def scale_heads(x: torch.Tensor, gate_logits: torch.Tensor, n_heads: int) -> tor
     return x
 
 
+def gate_heads(o: torch.Tensor, x: torch.Tensor, w_gate: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """o[t, h, :] *= sigmoid(x[t, :] . w_gate[h, :]) in place: ``small_linear_f32`` and ``scale_heads`` in one kernel
+    (the logits and the sigmoid in float32)."""
+    _req(o, "o", None, 2)
+    _req(x, "x", None, 2)
+    _req(w_gate, "w_gate", None, 2)
+    T, HD = o.shape
+    if HD % n_heads or x.shape[0] != T or tuple(w_gate.shape) != (n_heads, x.shape[1]):
+        raise ValueError("gate_heads: shapes do not agree")
+    _lib.check(_lib.load().qnn_gate_heads(_p(x), dt_code(x), _p(w_gate), dt_code(w_gate), x.shape[1], _p(o), dt_code(o), T,
+                                          n_heads, HD // n_heads, _stream()), "gate_heads")
+    return o
+
+
 def small_linear_f32(x: torch.Tensor, w: torch.Tensor, decay_bias: Optional[torch.Tensor] = None,
                      tau: Optional[float] = None) -> torch.Tensor:
     """x w^T with float32 sums and a float32 result, whatever the element types: for the few outputs that feed

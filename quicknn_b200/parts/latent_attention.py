@@ -107,7 +107,6 @@ class LatentAttentionMixer(AttentionMixer):
         T = x.shape[0]
         new = torch.empty if rp == r else torch.zeros              # columns behind the latent stay zero
         a = project(x, self.w_in)                                           # [T, q_rank + kv_rank]
-        gate = ops.small_linear_f32(x, self.w_gate)                         # [T, heads], float32
         cq = torch.empty((T, rq), dtype=a.dtype, device=a.device)
         ops.rmsnorm_cols(a, 0, rq, self.norm_q, self.eps, cq)
         q = project(cq, self.w_qk)                                          # [T, heads * rank]: queries on the latent's side
@@ -126,5 +125,5 @@ class LatentAttentionMixer(AttentionMixer):
             if step.mode == "prefill" and line.writes:
                 ops.cache_append(packed, H, 1, rp, step.tok_pos, step.tok_slot, line)
             o = self.attend(packed, step, line)
-        ops.scale_heads(o, gate, H)
+        ops.gate_heads(o, x, self.w_gate, H)                                # times sigmoid(w_g,h . x), float32
         return project(o, self.w_ov)

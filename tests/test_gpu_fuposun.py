@@ -187,6 +187,13 @@ def test_norms_over_pieces_of_rows_head_gates_and_float32_products():
     ops.scale_heads(t, dev(g), 3)
     ref = (o.reshape(6, 3, 10) * FP.sigmoid(g.astype(np.float64))[:, :, None]).reshape(6, 30)
     assert np.abs(host(t) - ref).max() < 1e-6
+    for width in (20, 100, 2304):                               # the gate's logits formed in the same kernel
+        xg, wg = bf(rnd((6, width), 9)), bf(rnd((3, width), 10, 0.2))
+        for dt in (torch.float32, torch.bfloat16):
+            t = dev(o)
+            ops.gate_heads(t, dev(xg, dt), dev(wg, dt), 3)
+            ref = (o.reshape(6, 3, 10) * FP.sigmoid(xg.astype(np.float64) @ wg.T.astype(np.float64))[:, :, None]).reshape(6, 30)
+            assert np.abs(host(t) - ref).max() < 1e-5
     for K in (5, 16, 100, 321):                                 # a thread per output, a warp per row
         a, b = bf(rnd((11, K), 6)), bf(rnd((7, K), 7))
         for dt in (torch.float32, torch.bfloat16):
