@@ -139,8 +139,10 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 // activation codes of the gated feed-forward
 #define QNN_ACT_GELU_TANH 0
 #define QNN_ACT_SILU 1
+#define QNN_ACT_RELU2 2          // the square of relu
+__device__ __forceinline__ float relu2(float x) { const float r = fmaxf(x, 0.f); return x == x ? r * r : x; }
 __device__ __forceinline__ float activate(float x, int act) {
-    return act == QNN_ACT_SILU ? silu(x) : gelu_tanh(x);
+    return act == QNN_ACT_SILU ? silu(x) : (act == QNN_ACT_RELU2 ? relu2(x) : gelu_tanh(x));
 }
 // The same for results that are rounded to bfloat16 anyway: the hardware tanh (error about
 // 2^-11, below bfloat16's rounding) and the fast exponential.
@@ -151,6 +153,7 @@ __device__ __forceinline__ float tanh_approx(float x) {
 }
 __device__ __forceinline__ float activate_fast(float x, int act) {
     if (act == QNN_ACT_SILU) return __fdividef(x, 1.f + __expf(-x));
+    if (act == QNN_ACT_RELU2) return relu2(x);
     return 0.5f * x * (1.f + tanh_approx(0.7978845608028654f * (x + 0.044715f * x * x * x)));
 }
 

@@ -9,6 +9,18 @@
 //                       into it: whole prompts, portions and single tokens are the same launch
 //   qnn_gla_norm_gate   per head: RMS norm of o over vdim with a weight shared by the heads, times silu(g)
 //
+// The same scan serves matrix memories whose decay is one number per head (a constant, or a gate): `decay_per_head`
+// reads decay[row, h] instead of decay[row, h*dim + i] (a row pitch of 0 gives every row the same decays), `kw`
+// multiplies the key of (row, head) by a float32 weight (an input gate) as it is staged, and `ones_col` names a value
+// column that is 1 in every row, so that its state column is the normaliser n_t = d_t n_{t-1} + w_t k_t and its output
+// n_t . q_t.  `state_stride` is the distance between two slots' states in floats (a slot may keep more than S).
+//
+//   qnn_mlstm_gates     from the pre-activations of an input and a forget gate per (row, head): the soft-capped log
+//                       gates, the running maximum m_t = max(f_t + m_{t-1}, i_t) from the slot's m and back into it,
+//                       and per row the decay exp(f_t + m_{t-1} - m_t), the key weight exp(i_t - m_t) and exp(-m_t)
+//   qnn_head_norm_gate  qnn_gla_norm_gate with its options: a denominator max(|n.q|, e) + 1e-6 first, the norm's weight
+//                       per column of a head, per column of the row, or none, and silu or sigmoid of the gate
+//
 // The scan: a block owns 64 (32 with more than 128 key channels) value columns of one (sequence, head).  Eight lanes
 // share a group of 4 (2) columns, each with an eighth of the key channels of the state in registers, so that what a
 // lane reads of q, k and the decay from shared memory serves several columns (with one column per lane the kernel
@@ -43,7 +55,8 @@ __global__ void __launch_bounds__(GLA_THREADS)
 gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long ld,
                 const float* __restrict__ decay, long long ldd, float q_scale, const int* __restrict__ seq_row0,
                 const int* __restrict__ seq_len, const int* __restrict__ slots, float* __restrict__ state,
-                float* __restrict__ out, long long ldo, int H, int dim, int vdim, int seg_len, int nseg) {
+                float* __restrict__ out, long long ldo, int H, int dim, int vdim, int seg_len, int nseg,
+                int decay_per_head, const float* __restrict__ kw, long long ldw, int ones_col, long long state_stride) {
     using C = GlaChunk<RPT, CPT>;
     constexpr int DIMP = RPT * GLA_SHARE;                    // key channels with padding
     constexpr bool AHEAD = RPT <= 16;                        // the next chunk's loads in registers while this one is walked
@@ -67,7 +80,8 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     const int part = threadIdx.x & (GLA_SHARE - 1), grp = threadIdx.x / GLA_SHARE;
     const int col = c0 + grp * CPT;                          // the first of this lane's columns
     float S[RPT][CPT];
-    float* my_state = state + (((size_t)(slot < 0 ? 0 : slot) * H + h) * dim) * vdim + col;
+    float* my_state = state + (size_t)(slot < 0 ? 0 : slot) * state_stride + ((size_t)h * dim) * vdim + col;
+    const int vreal = vdim - (ones_col >= 0 ? 1 : 0);       // value columns that the rows really hold
 #pragma unroll
     for (int r = 0; r < RPT; ++r)
 #pragma unroll
@@ -78,24 +92,27 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     // what is loaded stays as it came until `put`: a conversion here would wait for the load at once, and the loads
     // are meant to be in flight while the rows before them are walked
     T rq[C::PER_THREAD], rk[C::PER_THREAD], rv[C::V_PER_THREAD];
-    float ra[C::PER_THREAD];
+    float ra[C::PER_THREAD], rw[C::PER_THREAD];
     auto fetch = [&](int t0) {                               // global memory -> registers (rows beyond the sequence: nothing)
         const int nt = min(GLA_ROWS, n - t0);
 #pragma unroll
         for (int e = 0; e < C::PER_THREAD; ++e) {
             const int idx = threadIdx.x + e * GLA_THREADS, tt = idx / DIMP, i = idx - tt * DIMP;
-            rq[e] = from_f<T>(0.f); rk[e] = from_f<T>(0.f); ra[e] = 1.f;
+            rq[e] = from_f<T>(0.f); rk[e] = from_f<T>(0.f); ra[e] = 1.f; rw[e] = 1.f;
             if (tt < nt && i < dim) {
                 const size_t row = (size_t)(row0 + t0 + tt);
                 rq[e] = q[row * ld + h * dim + i];
                 rk[e] = k[row * ld + h * dim + i];
-                ra[e] = decay[row * ldd + h * dim + i];
+                ra[e] = decay[row * ldd + (decay_per_head ? h : h * dim + i)];
+                if (kw != nullptr) rw[e] = kw[row * ldw + h];
             }
         }
 #pragma unroll
         for (int e = 0; e < C::V_PER_THREAD; ++e) {
             const int idx = threadIdx.x + e * GLA_THREADS, tt = idx / C::COLS, c = idx - tt * C::COLS;
-            rv[e] = (tt < nt && c0 + c < vdim) ? v[(size_t)(row0 + t0 + tt) * ld + h * vdim + c0 + c] : from_f<T>(0.f);
+            rv[e] = from_f<T>(0.f);
+            if (tt < nt && c0 + c < vdim)
+                rv[e] = c0 + c == ones_col ? from_f<T>(1.f) : v[(size_t)(row0 + t0 + tt) * ld + h * vreal + c0 + c];
         }
     };
     auto put = [&](float* buf) {                             // registers -> shared memory
@@ -104,7 +121,7 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
             const int idx = threadIdx.x + e * GLA_THREADS, tt = idx / DIMP, i = idx - tt * DIMP;
             const int at = tt * C::ROW + (i / RPT) * C::PART + (i % RPT);
             buf[at] = to_f(rq[e]) * q_scale;
-            buf[C::ARRAY + at] = to_f(rk[e]);
+            buf[C::ARRAY + at] = to_f(rk[e]) * rw[e];
             buf[2 * C::ARRAY + at] = ra[e];
         }
 #pragma unroll
@@ -199,49 +216,124 @@ __global__ void gla_segment_decay_kernel(const float* __restrict__ decay, long l
 // A thread per state element of a sequence.
 __global__ void gla_segment_prefix_kernel(float* __restrict__ scratch, const float* __restrict__ D,
                                           const int* __restrict__ slots, float* __restrict__ state, int nseg, int dim,
-                                          int vdim, size_t per_seq) {
+                                          int vdim, size_t per_seq, int decay_per_head, long long state_stride) {
     pdl_wait();
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int b = blockIdx.y;
     if (e >= per_seq) return;
     const int slot = slots[b];
     if (slot < 0) return;
-    const size_t hi = e / vdim;                               // (head, key channel) = the decay's column
-    float carry = state[(size_t)slot * per_seq + e];
+    // the decay's column: (head, key channel), or the head alone
+    const size_t hi = decay_per_head ? e / ((size_t)dim * vdim) : e / vdim;
+    const size_t n_dec = decay_per_head ? per_seq / ((size_t)dim * vdim) : per_seq / vdim;
+    float carry = state[(size_t)slot * state_stride + e];
     for (int seg = 0; seg < nseg; ++seg) {
         const size_t z = (size_t)b * nseg + seg;
         const float L = scratch[z * per_seq + e];
         scratch[z * per_seq + e] = carry;
-        carry = D[z * (per_seq / vdim) + hi] * carry + L;
+        carry = D[z * n_dec + hi] * carry + L;
     }
-    state[(size_t)slot * per_seq + e] = carry;
+    state[(size_t)slot * state_stride + e] = carry;
 }
 
-// a warp per (row, head)
+// a warp per (row, head).  o: float32 rows of H heads, `hs` columns apart, of which the first vdim are normed; with `den`
+// (float32 [rows, ldden], one per head) a head is first divided by max(|o[vdim]|, den) + 1e-6, o[vdim] being the
+// normaliser's product with the query.  w_mode: 0 no weight, 1 a weight per column of a head (shared by the heads),
+// 2 a weight per column of the row.  gate_act: 0 silu, 1 sigmoid.
 template <typename T>
-__global__ void gla_norm_gate_kernel(const float* __restrict__ o, long long ldo, const void* __restrict__ w, int w_dt,
-                                     float eps, const T* __restrict__ g, long long ldg, T* __restrict__ out,
-                                     long long ld_out, int rows, int H, int vdim) {
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, long long ldo, int hs, const float* __restrict__ den,
+                                      long long ldden, const void* __restrict__ w, int w_dt, int w_mode, float eps,
+                                      const T* __restrict__ g, long long ldg, int gate_act, T* __restrict__ out,
+                                      long long ld_out, int rows, int H, int vdim) {
     pdl_wait();
     const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (unit >= rows * H) return;
     const int t = unit / H, h = unit - t * H;
-    const float* orow = o + (size_t)t * ldo + h * vdim;
+    const float* orow = o + (size_t)t * ldo + (size_t)h * hs;
+    float scale = 1.f;
+    if (den != nullptr) scale = 1.f / (fmaxf(fabsf(orow[vdim]), den[(size_t)t * ldden + h]) + 1e-6f);
     float ss = 0.f;
-    for (int j = lane; j < vdim; j += 32) ss += orow[j] * orow[j];
+    for (int j = lane; j < vdim; j += 32) {
+        const float v = orow[j] * scale;
+        ss += v * v;
+    }
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / (float)vdim + eps);
     for (int j = lane; j < vdim; j += 32) {
         const float gv = to_f(g[(size_t)t * ldg + h * vdim + j]);
-        out[(size_t)t * ld_out + h * vdim + j] = from_f<T>(orow[j] * inv * load_as_f(w, w_dt, j) * silu(gv));
+        const float wv = w_mode == 0 ? 1.f : load_as_f(w, w_dt, w_mode == 2 ? (size_t)h * vdim + j : (size_t)j);
+        const float ga = gate_act == 1 ? 1.f / (1.f + expf(-gv)) : silu(gv);
+        out[(size_t)t * ld_out + h * vdim + j] = from_f<T>(orow[j] * scale * inv * wv * ga);
     }
 }
+
+// ---- gates of a matrix memory with a running maximum ---------------------------------------------------------------
+// pre: float32 [rows, ldp] with the input gate's pre-activation of head h at column h and the forget gate's at H + h;
+// bias: [2H] (input gates, then forget gates).  i = cap tanh((pre_i + b_i) / cap); f = log sigmoid(cap tanh((pre_f +
+// b_f) / cap)).  m_t = max(f_t + m_{t-1}, i_t) is a linear recurrence over (max, +): a row is the map m -> max(m + a, b)
+// with (a, b) = (f, i), and two rows in a row compose to (a1 + a2, max(b1 + a2, b2)), so a warp scans 32 rows at a time
+// with shuffles.  gates: float32 [rows, 3H]: the decay exp(f_t + m_{t-1} - m_t), the key weight exp(i_t - m_t),
+// exp(-m_t).  A warp per (sequence, head); m of the slot's head at mstate[slot * state_stride + h].
+__global__ void mlstm_gates_kernel(const float* __restrict__ pre, long long ldp, const void* __restrict__ bias, int b_dt,
+                                   float cap, const int* __restrict__ seq_row0, const int* __restrict__ seq_len,
+                                   const int* __restrict__ slots, float* __restrict__ mstate, long long state_stride,
+                                   float* __restrict__ gates, int H, int B) {
+    pdl_wait();
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (unit >= B * H) return;
+    const int b = unit / H, h = unit - b * H;
+    const int slot = slots[b];
+    const int row0 = seq_row0 ? seq_row0[b] : b, n = seq_len ? seq_len[b] : 1;
+    const float bi = load_as_f(bias, b_dt, h), bf = load_as_f(bias, b_dt, H + h);
+    float m = slot >= 0 ? mstate[(size_t)slot * state_stride + h] : 0.f;
+    const size_t ldg = (size_t)3 * H;
+    for (int t0 = 0; t0 < n; t0 += 32) {
+        const int t = t0 + lane;
+        float gi = -INFINITY, gf = 0.f;                        // rows beyond the sequence change nothing: m -> max(m, -inf)
+        if (t < n) {
+            const float zi = pre[(size_t)(row0 + t) * ldp + h] + bi, zf = pre[(size_t)(row0 + t) * ldp + H + h] + bf;
+            gi = cap * tanhf(zi / cap);
+            const float c = cap * tanhf(zf / cap);
+            gf = fminf(c, 0.f) - log1pf(expf(-fabsf(c)));
+        }
+        float a = gf, bb = gi;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const float pa = __shfl_up_sync(0xffffffffu, a, off), pb = __shfl_up_sync(0xffffffffu, bb, off);
+            if (lane >= off) {
+                bb = fmaxf(pb + a, bb);
+                a = pa + a;
+            }
+        }
+        const float mt = fmaxf(m + a, bb);
+        float before = __shfl_up_sync(0xffffffffu, mt, 1);
+        if (lane == 0) before = m;
+        if (t < n) {
+            float* gr = gates + (size_t)(row0 + t) * ldg;
+            const bool live = slot >= 0;
+            gr[h] = live ? expf(gf + before - mt) : 0.f;
+            gr[H + h] = live ? expf(gi - mt) : 0.f;
+            gr[2 * H + h] = live ? expf(-mt) : 1.f;
+        }
+        m = __shfl_sync(0xffffffffu, mt, 31);
+    }
+    if (slot >= 0 && lane == 0) mstate[(size_t)slot * state_stride + h] = m;
+}
+
+struct ScanExtra {
+    int decay_per_head = 0;
+    const float* kw = nullptr;
+    long long ldw = 0;
+    int ones_col = -1;
+    long long state_stride = 0;         // 0: H * dim * vdim
+};
 
 template <typename T>
 int scan_launch(const void* q, const void* k, const void* v, long long ld, const float* decay, long long ldd, float q_scale,
                 const int* seq_row0, const int* seq_len, const int* slots, float* state, float* out, long long ldo, int B,
-                int H, int dim, int vdim, int seg_len, int nseg, cudaStream_t st) {
+                int H, int dim, int vdim, int seg_len, int nseg, cudaStream_t st, ScanExtra x = ScanExtra()) {
     const int rpt = (dim + GLA_SHARE - 1) / GLA_SHARE;
+    const long long stride = x.state_stride > 0 ? x.state_stride : (long long)H * dim * vdim;
 #define QNN_GLA(RPTV, CPTV)                                                                                          \
     {                                                                                                                \
         using C = GlaChunk<RPTV, CPTV>;                                                                              \
@@ -255,7 +347,7 @@ int scan_launch(const void* q, const void* k, const void* v, long long ld, const
         }                                                                                                            \
         launch_pdl(gla_scan_kernel<T, RPTV, CPTV>, grid, dim3(GLA_THREADS), smem, st, (const T*)q, (const T*)k,     \
                    (const T*)v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, H, dim, vdim,    \
-                   seg_len, nseg);                                                                                   \
+                   seg_len, nseg, x.decay_per_head, x.kw, x.ldw, x.ones_col, stride);                                \
     }
     if (rpt <= 4) QNN_GLA(4, 4)
     else if (rpt <= 8) QNN_GLA(8, 4)
@@ -264,6 +356,28 @@ int scan_launch(const void* q, const void* k, const void* v, long long ld, const
     else return QNN_ERR_UNSUPPORTED;
 #undef QNN_GLA
     QNN_LAUNCH_CHECK();
+}
+
+template <typename T>
+int scan_segments(const void* q, const void* k, const void* v, long long ld, const float* decay, long long ldd, float q_scale,
+                  const int* seq_row0, const int* seq_len, const int* slots, float* state, float* out, long long ldo, int B,
+                  int H, int dim, int vdim, int seg_len, int nseg, float* scratch, float* seg_decay, cudaStream_t st,
+                  ScanExtra x = ScanExtra()) {
+    const size_t per_seq = (size_t)H * dim * vdim;
+    const long long slot_stride = x.state_stride > 0 ? x.state_stride : (long long)per_seq;
+    ScanExtra in_scratch = x;
+    in_scratch.state_stride = (long long)per_seq;            // segment z's state is entry z of the scratch
+    int rc = scan_launch<T>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, scratch, nullptr, ldo, B, H, dim, vdim,
+                            seg_len, nseg, st, in_scratch);
+    if (rc != 0) return rc;
+    const int HD = x.decay_per_head ? H : H * dim;
+    launch_pdl(gla_segment_decay_kernel, dim3((HD + 127) / 128, B * nseg), dim3(128), 0, st, decay, ldd, seq_row0, seq_len,
+               seg_len, nseg, seg_decay, HD);
+    launch_pdl(gla_segment_prefix_kernel, dim3((unsigned)((per_seq + 255) / 256), B), dim3(256), 0, st, scratch,
+               (const float*)seg_decay, slots, state, nseg, dim, vdim, per_seq, x.decay_per_head, slot_stride);
+    if ((rc = (int)cudaGetLastError()) != 0) return rc;
+    return scan_launch<T>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, scratch, out, ldo, B, H, dim, vdim,
+                          seg_len, nseg, st, in_scratch);
 }
 
 }  // namespace
@@ -296,36 +410,81 @@ QNN_API int qnn_gla_scan_segments(const void* q, const void* k, const void* v, l
     if (H <= 0 || dim <= 0 || vdim <= 0 || H > 65535 || seg_len < 1 || nseg < 1 || (long long)B * nseg > 65535)
         return QNN_ERR_ARGUMENT;
     if (seq_row0 == nullptr || seq_len == nullptr) return QNN_ERR_ARGUMENT;
-    int rc;
-#define QNN_SCAN(STATE, OUT)                                                                                           \
-    (dtype == QNN_DT_BF16 ? scan_launch<bf16>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, STATE, OUT, ldo, \
-                                              B, H, dim, vdim, seg_len, nseg, st)                                      \
-                          : scan_launch<float>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, STATE, OUT, \
-                                               ldo, B, H, dim, vdim, seg_len, nseg, st))
-    if ((rc = QNN_SCAN(scratch, nullptr)) != 0) return rc;
-    const int HD = H * dim;
-    launch_pdl(gla_segment_decay_kernel, dim3((HD + 127) / 128, B * nseg), dim3(128), 0, st, decay, ldd, seq_row0, seq_len,
-               seg_len, nseg, seg_decay, HD);
-    const size_t per_seq = (size_t)H * dim * vdim;
-    launch_pdl(gla_segment_prefix_kernel, dim3((unsigned)((per_seq + 255) / 256), B), dim3(256), 0, st, scratch,
-               (const float*)seg_decay, slots, state, nseg, dim, vdim, per_seq);
-    if ((rc = (int)cudaGetLastError()) != 0) return rc;
-    return QNN_SCAN(scratch, out);
-#undef QNN_SCAN
+    if (dtype == QNN_DT_BF16)
+        return scan_segments<bf16>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim,
+                                   vdim, seg_len, nseg, scratch, seg_decay, st);
+    return scan_segments<float>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim, vdim,
+                                seg_len, nseg, scratch, seg_decay, st);
+}
+
+// The scan with one decay per (row, head): S_t = d_t S_{t-1} + w_t k_t v_t^T, o_t = S_t^T (q_t q_scale).
+// decay: float32, decay[row * ldd + h] (ldd = 0: the same H decays in every row); kw: the key weights w,
+// kw[row * ldw + h], or null for 1.  normaliser != 0: the state has one column more than the rows have value columns,
+// which is fed 1 in every row (n_t = d_t n_{t-1} + w_t k_t); out then has vdim + 1 columns per head, the last n_t . q_t.
+// state: the slot's [H, dim, vdim (+1)] floats start at state + slot * state_stride.  seg_len > 0: in segments, with
+// scratch [B * nseg, H, dim, vdim (+1)] zeroed by the caller and seg_decay [B * nseg, H].
+QNN_API int qnn_memory_scan(const void* q, const void* k, const void* v, long long ld, int dtype, const float* decay,
+                            long long ldd, const float* kw, long long ldw, float q_scale, int normaliser,
+                            const int* seq_row0, const int* seq_len, const int* slots, float* state, long long state_stride,
+                            float* out, long long ldo, int B, int H, int dim, int vdim, int seg_len, int nseg,
+                            float* scratch, float* seg_decay, cudaStream_t st) {
+    if (B <= 0) return 0;
+    if (H <= 0 || dim <= 0 || vdim <= 0 || H > 65535 || B > 65535) return QNN_ERR_ARGUMENT;
+    if ((seq_row0 == nullptr) != (seq_len == nullptr)) return QNN_ERR_ARGUMENT;
+    const int vs = vdim + (normaliser ? 1 : 0);
+    if (state_stride < (long long)H * dim * vs) return QNN_ERR_ARGUMENT;
+    ScanExtra x;
+    x.decay_per_head = 1;
+    x.kw = kw;
+    x.ldw = ldw;
+    x.ones_col = normaliser ? vdim : -1;
+    x.state_stride = state_stride;
+    if (seg_len > 0) {
+        if (nseg < 1 || (long long)B * nseg > 65535 || seq_row0 == nullptr || scratch == nullptr || seg_decay == nullptr)
+            return QNN_ERR_ARGUMENT;
+        if (dtype == QNN_DT_BF16)
+            return scan_segments<bf16>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim,
+                                       vs, seg_len, nseg, scratch, seg_decay, st, x);
+        return scan_segments<float>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim,
+                                    vs, seg_len, nseg, scratch, seg_decay, st, x);
+    }
+    if (dtype == QNN_DT_BF16)
+        return scan_launch<bf16>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim, vs,
+                                 0, 1, st, x);
+    return scan_launch<float>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim, vs, 0,
+                              1, st, x);
+}
+
+QNN_API int qnn_mlstm_gates(const float* pre, long long ldp, const void* bias, int b_dt, float cap, const int* seq_row0,
+                            const int* seq_len, const int* slots, float* mstate, long long state_stride, float* gates,
+                            int H, int B, cudaStream_t st) {
+    if (B <= 0) return 0;
+    if (H <= 0 || !(cap > 0.f) || (seq_row0 == nullptr) != (seq_len == nullptr)) return QNN_ERR_ARGUMENT;
+    const int warps = 4;
+    launch_pdl(mlstm_gates_kernel, dim3(((size_t)B * H + warps - 1) / warps), dim3(warps * 32), 0, st, pre, ldp, bias, b_dt,
+               cap, seq_row0, seq_len, slots, mstate, state_stride, gates, H, B);
+    QNN_LAUNCH_CHECK();
+}
+
+QNN_API int qnn_head_norm_gate(const float* o, long long ldo, int hs, const float* den, long long ldden, const void* w,
+                               int w_dt, int w_mode, float eps, const void* g, long long ldg, int gate_act, void* out,
+                               long long ld_out, int dtype, int rows, int H, int vdim, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    if (H <= 0 || vdim <= 0 || hs < vdim || (den != nullptr && hs <= vdim) || (w_mode != 0 && w == nullptr))
+        return QNN_ERR_ARGUMENT;
+    const int warps = 4;
+    const dim3 grid(((size_t)rows * H + warps - 1) / warps);
+    if (dtype == QNN_DT_BF16)
+        launch_pdl(head_norm_gate_kernel<bf16>, grid, dim3(warps * 32), 0, st, o, ldo, hs, den, ldden, w, w_dt, w_mode, eps,
+                   (const bf16*)g, ldg, gate_act, (bf16*)out, ld_out, rows, H, vdim);
+    else
+        launch_pdl(head_norm_gate_kernel<float>, grid, dim3(warps * 32), 0, st, o, ldo, hs, den, ldden, w, w_dt, w_mode, eps,
+                   (const float*)g, ldg, gate_act, (float*)out, ld_out, rows, H, vdim);
+    QNN_LAUNCH_CHECK();
 }
 
 QNN_API int qnn_gla_norm_gate(const float* o, long long ldo, const void* w, int w_dt, float eps, const void* g,
                               long long ldg, void* out, long long ld_out, int dtype, int rows, int H, int vdim,
                               cudaStream_t st) {
-    if (rows <= 0) return 0;
-    if (H <= 0 || vdim <= 0) return QNN_ERR_ARGUMENT;
-    const int warps = 4;
-    const dim3 grid(((size_t)rows * H + warps - 1) / warps);
-    if (dtype == QNN_DT_BF16)
-        launch_pdl(gla_norm_gate_kernel<bf16>, grid, dim3(warps * 32), 0, st, o, ldo, w, w_dt, eps, (const bf16*)g, ldg,
-                   (bf16*)out, ld_out, rows, H, vdim);
-    else
-        launch_pdl(gla_norm_gate_kernel<float>, grid, dim3(warps * 32), 0, st, o, ldo, w, w_dt, eps, (const float*)g, ldg,
-                   (float*)out, ld_out, rows, H, vdim);
-    QNN_LAUNCH_CHECK();
+    return qnn_head_norm_gate(o, ldo, vdim, nullptr, 0, w, w_dt, 1, eps, g, ldg, 0, out, ld_out, dtype, rows, H, vdim, st);
 }

@@ -1,0 +1,136 @@
+// What happens to the rows of a stacked q | k | v product before attention (or before a recurrence), in one kernel:
+//
+//   1. a bias over the packed row (optional);
+//   2. an RMS norm per head over the first `norm_dim` columns of every query and key head, with a weight per column
+//      that all heads share (optional; the heads may be carried wider than norm_dim, with zero columns behind);
+//   3. a rotation of the first `rot` columns of every query and key head by position * inv_freq[j], the pair of
+//      frequency j being columns (j, j + rot/2) (half-split) or (2j, 2j + 1) (interleaved);
+//   4. the row written back in place, or to another buffer of another element type (float32 rows for a recurrence
+//      whose inputs must not be rounded again);
+//   5. keys and values appended to a paged cache line (optional; ring aware like qnn_rope_cache_write).
+//
+// Everything between load and store is float32.  A block per token, a warp per head; the angles of a token are
+// formed once per block.  inv_freq comes from the host (float64 arithmetic, rounded once), so any rescaling of the
+// frequencies is the caller's business.
+#include "common.cuh"
+
+using namespace qnn;
+
+namespace {
+
+template <typename T>
+__global__ void head_prep_kernel(const T* src, long long lds, void* dst, int dst_dt, long long ldd,
+                                 int nq, int nk, int nv, int hd, int norm_dim, int rot, int interleaved,
+                                 const void* __restrict__ bias, int b_dt, const void* __restrict__ wq,
+                                 const void* __restrict__ wk, int w_dt, float eps, const float* __restrict__ inv_freq,
+                                 const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, T* __restrict__ k_pool,
+                                 T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages, int page_size,
+                                 int ring, const int* __restrict__ slot_len, int write_cache) {
+    extern __shared__ float sm[];                   // [rot/2] (cos, sin) pairs, then a head of hd floats per warp
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = tok_pos != nullptr ? tok_pos[t] : 0;
+    const int slot = tok_slot != nullptr ? tok_slot[t] : -1;
+    const int rh = rot / 2;
+    float2* angles = reinterpret_cast<float2*>(sm);
+    float* heads = sm + 2 * rh;
+    for (int j = threadIdx.x; j < rh; j += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[j], &sn, &cs);
+        angles[j] = make_float2(cs, sn);
+    }
+    __syncthreads();
+    size_t cache_base = 0;
+    bool wr = write_cache && slot >= 0;
+    // a prompt longer than the ring keeps only its last `ring` positions (the length after this step is slot_len)
+    if (wr && ring > 0 && pos + ring < slot_len[slot]) wr = false;
+    if (wr) {
+        const int r = ring > 0 ? pos % ring : pos;
+        const int page = page_table[(size_t)slot * max_pages + r / page_size];
+        cache_base = ((size_t)page * nk * page_size + (r % page_size)) * hd;
+    }
+    const size_t head_stride = (size_t)page_size * hd;
+    const T* row = src + (size_t)t * lds;
+    const size_t out_row = (size_t)t * ldd;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    float* mine = heads + (size_t)warp * hd;
+    for (int h = warp; h < nq + nk; h += nwarp) {
+        const bool is_k = h >= nq;
+        const size_t c0 = (size_t)h * hd;
+        float ss = 0.f;
+        for (int c = lane; c < hd; c += 32) {
+            float v = to_f(row[c0 + c]);
+            if (bias != nullptr) v += load_as_f(bias, b_dt, c0 + c);
+            mine[c] = v;
+            if (c < norm_dim) ss += v * v;
+        }
+        const void* w = is_k ? wk : wq;
+        if (w != nullptr) {
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)norm_dim + eps);
+            for (int c = lane; c < norm_dim; c += 32) mine[c] = mine[c] * inv * load_as_f(w, w_dt, c);
+        }
+        __syncwarp();
+        for (int j = lane; j < rh; j += 32) {
+            const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + rh;
+            const float a = mine[ia], b = mine[ib];
+            const float2 cs = angles[j];
+            mine[ia] = a * cs.x - b * cs.y;
+            mine[ib] = b * cs.x + a * cs.y;
+        }
+        __syncwarp();
+        T* cache = (is_k && wr) ? k_pool + cache_base + (size_t)(h - nq) * head_stride : nullptr;
+        for (int c = lane; c < hd; c += 32) {
+            const float v = mine[c];
+            store_from_f(dst, dst_dt, out_row + c0 + c, v);
+            if (cache != nullptr) cache[c] = from_f<T>(v);
+        }
+        __syncwarp();
+    }
+    // values: nv columns behind the keys (nv = kv heads x hd when they go to the cache)
+    const size_t v0 = (size_t)(nq + nk) * hd;
+    const bool v_cache = wr && v_pool != nullptr;
+    if (nv > 0 && (bias != nullptr || v_cache || (const void*)src != (const void*)dst)) {
+        for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+            float v = to_f(row[v0 + c]);
+            if (bias != nullptr) v += load_as_f(bias, b_dt, v0 + c);
+            store_from_f(dst, dst_dt, out_row + v0 + c, v);
+            if (v_cache) v_pool[cache_base + (size_t)(c / hd) * head_stride + (c % hd)] = from_f<T>(v);
+        }
+    }
+}
+
+}  // namespace
+
+// src: [T, lds] rows of `dtype` holding nq query heads, nk key heads (hd columns each) and nv value columns, in that
+// order; dst: the same layout with row pitch ldd in `dst_dt` (may be src itself).  bias: over the packed row, or null.
+// wq / wk: norm weights [norm_dim] of `w_dt`, or null.  inv_freq: [rot/2] float32.  The cache arguments are those of
+// qnn_rope_cache_write; with write_cache, nv must be nk * hd (or 0 with v_pool null) and dst_dt the pools' type.
+QNN_API int qnn_head_prep(const void* src, int dtype, long long lds, void* dst, int dst_dt, long long ldd, int T, int nq,
+                          int nk, int nv, int hd, int norm_dim, int rot, int interleaved, const void* bias, int b_dt,
+                          const void* wq, const void* wk, int w_dt, float eps, const float* inv_freq, const int* tok_pos,
+                          const int* tok_slot, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                          int page_size, int ring, const int* slot_len, int write_cache, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (nq < 0 || nk < 0 || nv < 0 || hd <= 0 || rot % 2 || rot < 0 || rot > hd || norm_dim < 0 || norm_dim > hd)
+        return QNN_ERR_ARGUMENT;
+    if ((wq != nullptr || wk != nullptr) && norm_dim == 0) return QNN_ERR_ARGUMENT;
+    if (rot > 0 && (inv_freq == nullptr || tok_pos == nullptr)) return QNN_ERR_ARGUMENT;
+    if (write_cache && (tok_slot == nullptr || k_pool == nullptr || page_table == nullptr || slot_len == nullptr ||
+                        (v_pool != nullptr && nv != nk * hd)))
+        return QNN_ERR_ARGUMENT;
+    const int heads = nq + nk;
+    int warps = heads >= 8 ? 8 : (heads >= 4 ? 4 : 2);
+    if (T > 1024 && warps > 4) warps = 4;
+    const size_t smem = ((size_t)rot + (size_t)warps * hd) * sizeof(float);
+    if (smem > 48 * 1024) return QNN_ERR_UNSUPPORTED;
+    if (dtype == QNN_DT_BF16)
+        launch_pdl(head_prep_kernel<bf16>, dim3(T), dim3(warps * 32), smem, st, (const bf16*)src, lds, dst, dst_dt, ldd, nq, nk,
+                   nv, hd, norm_dim, rot, interleaved, bias, b_dt, wq, wk, w_dt, eps, inv_freq, tok_pos, tok_slot,
+                   (bf16*)k_pool, (bf16*)v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache);
+    else
+        launch_pdl(head_prep_kernel<float>, dim3(T), dim3(warps * 32), smem, st, (const float*)src, lds, dst, dst_dt, ldd, nq,
+                   nk, nv, hd, norm_dim, rot, interleaved, bias, b_dt, wq, wk, w_dt, eps, inv_freq, tok_pos, tok_slot,
+                   (float*)k_pool, (float*)v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache);
+    QNN_LAUNCH_CHECK();
+}

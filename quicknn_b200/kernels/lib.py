@@ -86,6 +86,21 @@ _SIGNATURES: Dict[str, list] = {
                         c_float, c_float, c_vp, c_vp],
     "qnn_moe_combine": [c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_vp],
     "qnn_gated_act_clamped": [c_vp, c_vp, c_int, c_int, c_int, c_float, c_float, c_vp],
+    "qnn_layernorm": [c_vp, c_int, c_vp, c_int, c_float, c_vp, c_int, c_int, c_int, c_vp],
+    "qnn_add_layernorm": [c_vp, c_vp, c_int, c_vp, c_int, c_vp, c_int, c_float, c_vp, c_int, c_int, c_int, c_vp],
+    "qnn_mean_rmsnorm": [c_vp, c_vp, c_int, c_int, c_int, c_float, c_vp, c_int, c_int, c_int, c_vp],
+    "qnn_add_mean_layernorm": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_float, c_vp, c_int, c_float, c_vp, c_int, c_int,
+                               c_int, c_vp],
+    "qnn_add_bias": [c_vp, c_int, c_vp, c_int, c_int, c_int, c_vp],
+    "qnn_activation": [c_vp, c_int, c_vp, c_int, c_ll, c_vp],
+    "qnn_head_prep": [c_vp, c_int, c_ll, c_vp, c_int, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_vp, c_int, c_vp, c_vp, c_int, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int,
+                      c_vp, c_int, c_vp],
+    "qnn_memory_scan": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_vp, c_ll, c_float, c_int, c_vp, c_vp, c_vp, c_vp,
+                        c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp],
+    "qnn_mlstm_gates": [c_vp, c_ll, c_vp, c_int, c_float, c_vp, c_vp, c_vp, c_vp, c_ll, c_vp, c_int, c_int, c_vp],
+    "qnn_head_norm_gate": [c_vp, c_ll, c_int, c_vp, c_ll, c_vp, c_int, c_int, c_float, c_vp, c_ll, c_int, c_vp, c_ll,
+                           c_int, c_int, c_int, c_int, c_vp],
 }
 
 ERR_UNSUPPORTED, ERR_ARGUMENT = 10001, 10002

@@ -22,7 +22,7 @@ from . import lib as _lib
 
 F32, BF16 = 0, 1
 EPI_NONE, EPI_SOFTCAP, EPI_GATED = 0, 1, 2
-ACT_CODES = {"gelu_tanh": 0, "silu": 1}
+ACT_CODES = {"gelu_tanh": 0, "silu": 1, "relu2": 2}
 SKINNY_MAX_ROWS = 64
 
 
@@ -1063,4 +1063,258 @@ def gated_act_clamped(gu: torch.Tensor, limit: float, alpha: float) -> torch.Ten
     out = torch.empty((T, I2 // 2), dtype=gu.dtype, device=gu.device)
     _lib.check(_lib.load().qnn_gated_act_clamped(_p(gu), _p(out), dt_code(gu), T, I2 // 2, float(limit), float(alpha),
                                                  _stream()), "gated_act_clamped")
+    return out
+
+
+# ---- layer norm, post-norm residual stream, branches side by side -------------------------------------------------------
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """(x - mean) / sqrt(var + eps) * weight over every row, float32 sums (var: the mean of the squared deviations)."""
+    _req(x, "x", None, 2)
+    _req(weight, "weight", None, 1)
+    T, H = x.shape
+    if weight.numel() != H:
+        raise ValueError(f"norm weight has {weight.numel()} elements for width {H}")
+    out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+    _lib.check(_lib.load().qnn_layernorm(_p(x), dt_code(x), _p(weight), dt_code(weight), float(eps), _p(out), dt_code(out),
+                                         T, H, _stream()), "layernorm")
+    return out
+
+
+def add_layernorm(resid: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                  bias: Optional[torch.Tensor] = None, copy_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """resid += layernorm(y + bias) * weight (float32 stream, in place).  With ``copy_dtype`` the new stream is
+    also returned in that element type (the stream itself when that is float32): what the next sublayer reads."""
+    _req(resid, "resid", torch.float32, 2)
+    _req(y, "y", None, 2)
+    _req(weight, "weight", None, 1)
+    T, H = resid.shape
+    if tuple(y.shape) != (T, H) or weight.numel() != H or (bias is not None and bias.numel() != H):
+        raise ValueError("add_layernorm: shapes do not agree")
+    copy = None
+    if copy_dtype is not None and copy_dtype != torch.float32:
+        copy = torch.empty((T, H), dtype=copy_dtype, device=resid.device)
+    _lib.check(_lib.load().qnn_add_layernorm(
+        _p(resid), _p(y), dt_code(y), _p(bias), dt_code(bias) if bias is not None else 0, _p(weight), dt_code(weight),
+        float(eps), _p(copy), dt_code(copy) if copy is not None else 0, T, H, _stream()), "add_layernorm")
+    return resid if (copy_dtype == torch.float32) else copy
+
+
+def _pointer_array(ts):
+    return (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+
+
+def _check_branches(ys, ws, what: str):
+    if not (1 <= len(ys) <= 4) or len(ws) != len(ys):
+        raise ValueError(f"{what}: one to four branches, a weight each")
+    T, H = ys[0].shape
+    for y, w in zip(ys, ws):
+        _req(y, "branch", ys[0].dtype, 2)
+        _req(w, "branch weight", ws[0].dtype, 1)
+        if tuple(y.shape) != (T, H) or w.numel() != H:
+            raise ValueError(f"{what}: shapes do not agree")
+    return T, H
+
+
+def mean_rmsnorm(ys, ws, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """(1/n) sum_b ys[b] / sqrt(mean(ys[b]^2) + eps) * ws[b] over every row: branches that ran side by side, each
+    RMS-normed with a plain weight, averaged.  float32 math."""
+    T, H = _check_branches(ys, ws, "mean_rmsnorm")
+    out = torch.empty((T, H), dtype=out_dtype, device=ys[0].device)
+    _lib.check(_lib.load().qnn_mean_rmsnorm(_pointer_array(ys), _pointer_array(ws), len(ys), dt_code(ys[0]), dt_code(ws[0]),
+                                            float(eps), _p(out), dt_code(out), T, H, _stream()), "mean_rmsnorm")
+    return out
+
+
+def add_mean_layernorm(resid: torch.Tensor, ys, ws, eps_branch: float, weight: torch.Tensor, eps: float,
+                       copy_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """``add_layernorm(resid, mean_rmsnorm(ys, ws), weight)`` in one kernel; the mean is never rounded."""
+    _req(resid, "resid", torch.float32, 2)
+    T, H = _check_branches(ys, ws, "add_mean_layernorm")
+    if tuple(resid.shape) != (T, H) or weight.numel() != H:
+        raise ValueError("add_mean_layernorm: shapes do not agree")
+    copy = None
+    if copy_dtype is not None and copy_dtype != torch.float32:
+        copy = torch.empty((T, H), dtype=copy_dtype, device=resid.device)
+    _lib.check(_lib.load().qnn_add_mean_layernorm(
+        _p(resid), _pointer_array(ys), _pointer_array(ws), len(ys), dt_code(ys[0]), dt_code(ws[0]), float(eps_branch),
+        _p(weight), dt_code(weight), float(eps), _p(copy), dt_code(copy) if copy is not None else 0, T, H, _stream()),
+        "add_mean_layernorm")
+    return resid if (copy_dtype == torch.float32) else copy
+
+
+def add_bias_(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """y[t, :] += bias, in place."""
+    _req(y, "y", None, 2)
+    _req(bias, "bias", None, 1)
+    if bias.numel() != y.shape[1]:
+        raise ValueError("add_bias_: one bias per column")
+    _lib.check(_lib.load().qnn_add_bias(_p(y), dt_code(y), _p(bias), dt_code(bias), y.shape[0], y.shape[1], _stream()),
+               "add_bias")
+    return y
+
+
+def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """act(x) elementwise, one of ``ACT_CODES`` (float32 math)."""
+    _req(x, "x")
+    out = torch.empty_like(x)
+    _lib.check(_lib.load().qnn_activation(_p(x), dt_code(x), _p(out), ACT_CODES[kind], x.numel(), _stream()), "activation")
+    return out
+
+
+# ---- the rows of a stacked q | k | v product on their way to attention or to a recurrence ----------------------------
+
+def head_prep(src: torch.Tensor, col0: int, n_q: int, n_k: int, n_v_cols: int, head_dim: int, *,
+              dst: Optional[torch.Tensor] = None, dst_col0: int = 0, bias: Optional[torch.Tensor] = None,
+              q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None, norm_dim: int = 0,
+              eps: float = 0.0, rot_dim: int = 0, inv_freq: Optional[torch.Tensor] = None, interleaved: bool = False,
+              tok_pos: Optional[torch.Tensor] = None, tok_slot: Optional[torch.Tensor] = None, line=None,
+              append: bool = False) -> torch.Tensor:
+    """Bias, an RMS norm per head of queries and keys, rotation and the append to a cache line, in one kernel.
+
+    ``src``: rows that hold, from column ``col0`` on, ``n_q`` query heads and ``n_k`` key heads of ``head_dim`` columns
+    and then ``n_v_cols`` value columns.  ``dst`` (default: in place) gets the same layout from ``dst_col0`` on in its
+    own element type.  ``bias``: over those columns.  ``q_norm`` / ``k_norm``: weights [norm_dim] of a norm over the
+    first ``norm_dim`` columns of each head.  ``rot_dim``: rotated columns per head, by ``tok_pos * inv_freq``, pairs
+    (j, j + rot_dim/2) or, ``interleaved``, (2j, 2j + 1).  ``append``: keys and values go to ``line``."""
+    _req(src, "src", None, 2)
+    T = src.shape[0]
+    width = (n_q + n_k) * head_dim + n_v_cols
+    if col0 + width > src.shape[1]:
+        raise ValueError("head_prep: the heads do not fit the rows")
+    if dst is None:
+        dst, dst_col0 = src, col0
+    _req(dst, "dst", None, 2)
+    if dst.shape[0] != T or dst_col0 + width > dst.shape[1]:
+        raise ValueError("head_prep: the destination does not fit")
+    if bias is not None:
+        _req(bias, "bias", None, 1)
+        if bias.numel() != width:
+            raise ValueError(f"head_prep: the bias has {bias.numel()} elements for {width} columns")
+    wdt = 0
+    for w in (q_norm, k_norm):
+        if w is not None:
+            _req(w, "norm weight", None, 1)
+            if w.numel() != norm_dim:
+                raise ValueError("head_prep: a norm weight per normed column")
+            wdt = dt_code(w)
+    if q_norm is not None and k_norm is not None and q_norm.dtype != k_norm.dtype:
+        raise TypeError("head_prep: the two norm weights have one element type")
+    if rot_dim:
+        _req(inv_freq, "inv_freq", torch.float32, 1)
+        _req(tok_pos, "tok_pos", torch.int32, 1)
+        if inv_freq.numel() != rot_dim // 2 or tok_pos.numel() < T:
+            raise ValueError("head_prep: a frequency per rotated pair and a position per row")
+    k_pool = v_pool = table = slot_len = None
+    max_pages = page_size = ring = 0
+    if append:
+        if dst.dtype != line.k.dtype:
+            raise TypeError("head_prep: rows that go to the cache have the cache's element type")
+        _req(tok_slot, "tok_slot", torch.int32, 1)
+        k_pool, v_pool = line.k, (line.v if line.has_values else None)
+        if tuple(k_pool.shape[1:]) != (n_k, line.page_size, head_dim):
+            raise ValueError(f"head_prep: the cache line is {tuple(k_pool.shape)}, the keys [*, {n_k}, {line.page_size}, {head_dim}]")
+        table, slot_len, max_pages = line.page_table, line.slot_len, line.page_table.shape[1]
+        page_size, ring = line.page_size, line.ring
+    _lib.check(_lib.load().qnn_head_prep(
+        _col_ptr(src, col0), dt_code(src), src.shape[1], _col_ptr(dst, dst_col0), dt_code(dst), dst.shape[1], T, n_q, n_k,
+        n_v_cols, head_dim, int(norm_dim), int(rot_dim), int(interleaved), _p(bias), dt_code(bias) if bias is not None else 0,
+        _p(q_norm), _p(k_norm), wdt, float(eps), _p(inv_freq) if rot_dim else None, _p(tok_pos), _p(tok_slot), _p(k_pool),
+        _p(v_pool), _p(table), max_pages, page_size, ring, _p(slot_len), int(append), _stream()), "head_prep")
+    return dst
+
+
+# ---- matrix memories with one decay per head ------------------------------------------------------------------------------
+
+def memory_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, decay_ld: int,
+                key_weight: Optional[torch.Tensor], kw_col: int, q_scale: float, normaliser: bool,
+                seq_row0: Optional[torch.Tensor],
+                seq_len: Optional[torch.Tensor], slots: torch.Tensor, state: torch.Tensor, n_seqs: int, n_heads: int,
+                dim: int, vdim: int, longest: int = 0) -> torch.Tensor:
+    """S_t = d_t S_{t-1} + w_t k_t v_t^T, o_t = S_t^T (q_t q_scale) over the rows of every sequence in order, from
+    the state of the sequence's slot and back into it; d and w are one float32 number per (row, head).
+
+    ``decay``: float32 with the decay of (row, head) at ``decay[row * decay_ld + head]`` (``decay_ld`` 0: a constant
+    per head); ``key_weight``: float32 rows with the weights of a row's heads from column ``kw_col`` on, or None for 1.  ``normaliser``: the state has a column more
+    than v, fed 1 in every row (n_t = d_t n_{t-1} + w_t k_t); the result then has vdim + 1 columns per head, the last
+    being n_t . q_t.  ``state``: float32 [slots, floats per slot], a slot's [heads, dim, vdim (+1)] first.  Returns
+    float32 [rows, heads * (vdim (+1))].  Long sequences run in segments side by side like ``gla_scan``."""
+    _req(proj, "proj", None, 2)
+    _req(decay, "decay", torch.float32)
+    _req(slots, "slots", torch.int32, 1)
+    _req(state, "state", torch.float32, 2)
+    T = proj.shape[0]
+    vs = vdim + (1 if normaliser else 0)
+    if state.shape[1] < n_heads * dim * vs or slots.numel() < n_seqs:
+        raise ValueError("memory_scan: the state is too small or there are fewer slots than sequences")
+    if (seq_row0 is None) != (seq_len is None):
+        raise ValueError("memory_scan: first rows and row counts come together")
+    if key_weight is not None:
+        _req(key_weight, "key_weight", torch.float32, 2)
+        if kw_col + n_heads > key_weight.shape[1] or key_weight.shape[0] != T:
+            raise ValueError("memory_scan: a key weight per (row, head)")
+    ldw = 0 if key_weight is None else key_weight.shape[1]
+    out = torch.empty((T, n_heads * vs), dtype=torch.float32, device=proj.device)
+    seg_len = nseg = 0
+    scratch = seg_decay = None
+    if seq_row0 is not None and longest >= GLA_SEGMENTS_FROM and n_seqs * -(-longest // GLA_SEGMENT) <= 65535:
+        seg_len, nseg = GLA_SEGMENT, -(-longest // GLA_SEGMENT)
+        scratch = torch.zeros((n_seqs * nseg, n_heads * dim * vs), dtype=torch.float32, device=proj.device)
+        seg_decay = torch.empty((n_seqs * nseg, n_heads), dtype=torch.float32, device=proj.device)
+    _lib.check(_lib.load().qnn_memory_scan(
+        _col_ptr(proj, q_col), _col_ptr(proj, k_col), _col_ptr(proj, v_col), proj.shape[1], dt_code(proj), _p(decay),
+        int(decay_ld), _col_ptr(key_weight, kw_col) if key_weight is not None else None, ldw, float(q_scale), int(normaliser), _p(seq_row0), _p(seq_len), _p(slots), _p(state),
+        state.shape[1], _p(out), out.shape[1], n_seqs, n_heads, dim, vdim, seg_len, nseg, _p(scratch), _p(seg_decay),
+        _stream()), "memory_scan", 4 if seg_len else 1)
+    return out
+
+
+def mlstm_gates(pre: torch.Tensor, bias: torch.Tensor, cap: float, seq_row0: Optional[torch.Tensor],
+                seq_len: Optional[torch.Tensor], slots: torch.Tensor, state: torch.Tensor, m_offset: int, n_seqs: int,
+                n_heads: int) -> torch.Tensor:
+    """From the pre-activations ``pre`` (float32 [rows, 2 heads]: input gates, then forget gates) and ``bias`` [2 heads]:
+    i = cap tanh(. / cap), f = log sigmoid(cap tanh(. / cap)), the running maximum m_t = max(f_t + m_{t-1}, i_t) from
+    the slot's m (``state[slot, m_offset + head]``) and back into it, and per (row, head) the decay
+    exp(f_t + m_{t-1} - m_t), the key weight exp(i_t - m_t) and exp(-m_t): float32 [rows, 3 heads]."""
+    _req(pre, "pre", torch.float32, 2)
+    _req(bias, "bias", None, 1)
+    _req(slots, "slots", torch.int32, 1)
+    _req(state, "state", torch.float32, 2)
+    T = pre.shape[0]
+    if pre.shape[1] != 2 * n_heads or bias.numel() != 2 * n_heads or m_offset + n_heads > state.shape[1]:
+        raise ValueError("mlstm_gates: shapes do not agree")
+    gates = torch.empty((T, 3 * n_heads), dtype=torch.float32, device=pre.device)
+    _lib.check(_lib.load().qnn_mlstm_gates(
+        _p(pre), pre.shape[1], _p(bias), dt_code(bias), float(cap), _p(seq_row0), _p(seq_len), _p(slots),
+        ctypes.c_void_p(state.data_ptr() + 4 * m_offset), state.shape[1], _p(gates), n_heads, n_seqs, _stream()),
+        "mlstm_gates")
+    return gates
+
+
+def head_norm_gate(o: torch.Tensor, head_stride: int, n_heads: int, vdim: int, eps: float, gate: torch.Tensor, g_col: int,
+                   gate_act: str, weight: Optional[torch.Tensor] = None, den: Optional[torch.Tensor] = None,
+                   den_col: int = 0) -> torch.Tensor:
+    """Per head of ``o`` (float32 [rows, heads * head_stride]): divided by max(|o[vdim]|, den) + 1e-6 when ``den``
+    (float32 rows, one number per head from column ``den_col`` on) is given; an RMS norm over the first ``vdim``
+    columns; times ``weight`` ([vdim]: shared by the heads, [heads * vdim]: per column of the row, None: none); times
+    silu or sigmoid of the gate columns of ``gate`` (from ``g_col`` on).  Returns [rows, heads * vdim] of gate's type."""
+    _req(o, "o", torch.float32, 2)
+    _req(gate, "gate", None, 2)
+    T = o.shape[0]
+    if o.shape[1] != n_heads * head_stride or gate.shape[0] != T or g_col + n_heads * vdim > gate.shape[1]:
+        raise ValueError("head_norm_gate: shapes do not agree")
+    mode = 0
+    if weight is not None:
+        _req(weight, "weight", None, 1)
+        mode = 1 if weight.numel() == vdim and n_heads > 1 else (2 if weight.numel() == n_heads * vdim else -1)
+        if mode < 0:
+            raise ValueError("head_norm_gate: the weight has vdim or heads * vdim elements")
+    if den is not None:
+        _req(den, "den", torch.float32, 2)
+    out = torch.empty((T, n_heads * vdim), dtype=gate.dtype, device=o.device)
+    _lib.check(_lib.load().qnn_head_norm_gate(
+        _p(o), o.shape[1], head_stride, _col_ptr(den, den_col) if den is not None else None,
+        den.shape[1] if den is not None else 0, _p(weight), dt_code(weight) if weight is not None else 0, mode, float(eps),
+        _col_ptr(gate, g_col), gate.shape[1], {"silu": 0, "sigmoid": 1}[gate_act], _p(out), out.shape[1], dt_code(gate), T,
+        n_heads, vdim, _stream()), "head_norm_gate")
     return out

@@ -8,6 +8,18 @@ and window; output projection.  The three projections are one product against th
 stacked matrix; rotation and append belong to the position part (one kernel, or, for the
 few rows of a decode step, the epilogue of that product).
 
+Options beyond that (all off unless the spec gives them):
+
+* ``v_head_dim``: a value size that differs from the key size ``head_dim``.  Heads are carried at one internal size,
+  the larger of the two rounded up to a whole 16-byte piece, with zero rows in the stacked matrix behind the shorter
+  kind (zero query/key columns add nothing to a score, zero value columns meet zero columns of the output matrix), so
+  every attention kernel of the library serves them; the cache line has the internal size.
+* ``bias``: biases on the q, k, v and o products (``q_bias`` ... ``o_bias``).
+* ``qk_norm`` = {"eps": e}: an RMS norm over ``head_dim`` per query head and key head with the weights ``q_norm`` /
+  ``k_norm`` (shared by the heads), before the rotation.
+* ``shared_kv``: the layer has no keys and values of its own; its schedule entry reads the cache line that another
+  layer writes (whose head counts, sizes and rotation are the same), with its own queries.
+
 Decode attention cuts each sequence's keys into ranges that run as separate blocks and are
 merged afterwards; how many ranges, and the scratch that the partial results need, are
 decided here (``tuning["decode_splits"]`` fixes the number).
@@ -19,7 +31,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from ..kernels import ops
-from .base import MIXERS, POSITIONS, CacheNeed, HeadShape, Mixer
+from .base import MIXERS, POSITIONS, CacheNeed, HeadPrep, HeadShape, Mixer
 from .linear import project, stack_rows
 from .spec import PartSpec
 
@@ -42,24 +54,78 @@ class AttentionMixer(Mixer):
         self.window = p.get("window")
         if self.n_heads % self.n_kv:
             raise ValueError(f"{self.n_kv} kv heads do not divide {self.n_heads} heads")
-        self.heads = HeadShape(self.n_heads, self.n_kv, self.head_dim)
+        # key size and value size as the checkpoint has them; `head_dim` from here on is the size heads are carried at
+        self.key_dim = self.head_dim
+        self.value_dim = int(p.get("v_head_dim") or self.head_dim)
+        self.has_bias = bool(p.get("bias", False))
+        self.qk_norm = p.get("qk_norm")
+        self.shared_kv = bool(p.get("shared_kv", False))
+        if p.get("v_head_dim") and (self.value_dim != self.key_dim or self.key_dim % 8):
+            self.head_dim = (max(self.key_dim, self.value_dim) + 7) // 8 * 8
+        self.heads = HeadShape(self.n_heads, 0 if self.shared_kv else self.n_kv, self.head_dim)
         pos: PartSpec = p["position"]
+        if self.head_dim != self.key_dim and "head_dim" in pos.params:
+            pos = PartSpec(pos.kind, dict(pos.params, head_dim=self.head_dim,
+                                          rotary_dim=pos.get("rotary_dim", self.key_dim)))
         self.position = POSITIONS.get(pos.kind)(pos)
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
+        self.out_bias: Optional[torch.Tensor] = None
+        # a block that adds the output's bias in its own kernel (with the norm and the add that follow) sets this
+        self.defer_out_bias = False
+        self.prep: Optional[HeadPrep] = None
         self._resident = 148
 
     @classmethod
     def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         p = spec.params
         H, nq, nkv, hd = int(p["hidden_size"]), int(p["n_heads"]), int(p["n_kv_heads"]), int(p["head_dim"])
-        M = cls.PARAM_ROLE_MATRIX
-        return {"q_proj": ((nq * hd, H), M), "k_proj": ((nkv * hd, H), M), "v_proj": ((nkv * hd, H), M),
-                "o_proj": ((H, nq * hd), M)}
+        vd = int(p.get("v_head_dim") or hd)
+        M, B, S = cls.PARAM_ROLE_MATRIX, cls.PARAM_ROLE_NORM, cls.PARAM_ROLE_SCALE
+        shared = bool(p.get("shared_kv", False))
+        out = {"q_proj": ((nq * hd, H), M), "o_proj": ((H, nq * vd), M)}
+        if not shared:
+            out.update({"k_proj": ((nkv * hd, H), M), "v_proj": ((nkv * vd, H), M)})
+        if p.get("bias", False):
+            out.update({"q_bias": ((nq * hd,), B), "o_bias": ((H,), B)})
+            if not shared:
+                out.update({"k_bias": ((nkv * hd,), B), "v_bias": ((nkv * vd,), B)})
+        if p.get("qk_norm"):
+            out["q_norm"] = ((hd,), S)
+            if not shared:
+                out["k_norm"] = ((hd,), S)
+        return out
+
+    def _carried(self, t: torch.Tensor, heads: int, size: int) -> torch.Tensor:
+        """Rows (or elements) of ``heads`` heads of ``size`` each, laid out at the carried head size with zeros behind."""
+        if size == self.head_dim:
+            return t
+        out = torch.zeros((heads, self.head_dim) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        out[:, :size] = t.reshape((heads, size) + tuple(t.shape[1:]))
+        return out.reshape((heads * self.head_dim,) + tuple(t.shape[1:]))
 
     def load(self, tensors, compute_dtype, device) -> None:
-        self.w_qkv = stack_rows([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]])
-        self.w_o = tensors["o_proj"].contiguous()
+        kd, vd, D = self.key_dim, self.value_dim, self.head_dim
+        parts = [self._carried(tensors["q_proj"], self.n_heads, kd)]
+        biases = [self._carried(tensors["q_bias"], self.n_heads, kd)] if self.has_bias else []
+        if not self.shared_kv:
+            parts += [self._carried(tensors["k_proj"], self.n_kv, kd), self._carried(tensors["v_proj"], self.n_kv, vd)]
+            if self.has_bias:
+                biases += [self._carried(tensors["k_bias"], self.n_kv, kd), self._carried(tensors["v_bias"], self.n_kv, vd)]
+        self.w_qkv = stack_rows(parts)
+        w_o = tensors["o_proj"]
+        if vd != D:                                          # zero columns where the carried values are zero
+            wide = torch.zeros((w_o.shape[0], self.n_heads, D), dtype=w_o.dtype, device=w_o.device)
+            wide[:, :, :vd] = w_o.reshape(w_o.shape[0], self.n_heads, vd)
+            w_o = wide.reshape(w_o.shape[0], self.n_heads * D)
+        self.w_o = w_o.contiguous()
+        self.out_bias = tensors["o_bias"].contiguous() if self.has_bias else None
+        if self.has_bias or self.qk_norm:
+            self.prep = HeadPrep(
+                bias=torch.cat([b.to(torch.float32) for b in biases]).contiguous() if biases else None,
+                q_norm=tensors["q_norm"].contiguous() if self.qk_norm else None,
+                k_norm=tensors["k_norm"].contiguous() if self.qk_norm and not self.shared_kv else None,
+                norm_dim=kd if self.qk_norm else 0, eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
         self.position.prepare(device)
         # sizes that the kernels do not take are refused here, when the model is built, not at its first step
         why = (ops.attention_refusal(compute_dtype, self.n_heads, self.n_kv, self.head_dim)
@@ -74,7 +140,10 @@ class AttentionMixer(Mixer):
         self._resident = sms * max(1, min(8, 512 // max(1, self.head_dim)))
 
     def weight_bytes(self) -> int:
-        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o))
+        ws = [self.w_qkv, self.w_o, self.out_bias]
+        if self.prep is not None:
+            ws += [self.prep.bias, self.prep.q_norm, self.prep.k_norm]
+        return sum(w.numel() * w.element_size() for w in ws if w is not None)
 
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed(self.n_kv, self.head_dim, self.window)
@@ -131,11 +200,16 @@ class AttentionMixer(Mixer):
     def forward(self, x: torch.Tensor, step, line) -> torch.Tensor:
         h = self.heads
         extend = step.mode == "extend"
-        qkv = None if extend else self.position.project_and_place(x, self.w_qkv, h, step, line)
+        fusable = not extend and self.prep is None and not self.shared_kv
+        qkv = self.position.project_and_place(x, self.w_qkv, h, step, line) if fusable else None
         if qkv is None:
             qkv = project(x, self.w_qkv)
-            self.position.place(qkv, h, step, line, append=not extend)
-        return project(self.attend(qkv, step, line), self.w_o)
+            if self.prep is None:
+                self.position.place(qkv, h, step, line, append=not extend)
+            else:
+                self.position.place(qkv, h, step, line, append=not extend, prep=self.prep)
+        y = project(self.attend(qkv, step, line), self.w_o)
+        return y if (self.out_bias is None or self.defer_out_bias) else ops.add_bias_(y, self.out_bias)
 
     def attend(self, qkv: torch.Tensor, step, line) -> torch.Tensor:
         """Attention of the packed q|k|v rows of a step, by the step's mode.  In prefill and decode the keys and
@@ -150,7 +224,7 @@ class AttentionMixer(Mixer):
                                 line.page_size, line.ring, step.tok_pos, step.tok_row0, step.tok_slot, self.scale,
                                 self.softcap, self.window, whole=getattr(step, "whole", None))
             ops.cache_append(qkv, h.n_heads, h.n_kv_heads, h.head_dim, step.tok_pos, step.tok_slot, line)
-        elif step.mode != "decode" and not line.writes:
+        elif step.mode != "decode" and (not line.writes or self.shared_kv):
             # the keys of this line were written by another layer earlier in this step; in a ring the last
             # rows of the step have by then overwritten cells: whole prompts may fill the ring, a step that
             # continues a sequence may bring only as many rows as the ring has cells beyond the window

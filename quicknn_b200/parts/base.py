@@ -107,6 +107,19 @@ class HeadShape:
         return (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
 
 
+@dataclasses.dataclass
+class HeadPrep:
+    """What a mixer wants done to the packed q|k|v rows before their positions are placed: a bias over the packed row
+    (None: none) and an RMS norm over the first ``norm_dim`` columns of every query and key head with the weights
+    ``q_norm`` / ``k_norm`` (None: no norm).  Tensors on the device."""
+
+    bias: Any = None
+    q_norm: Any = None
+    k_norm: Any = None
+    norm_dim: int = 0
+    eps: float = 0.0
+
+
 class Part:
     """Common base: parameters by local name."""
 
@@ -157,10 +170,13 @@ class Positions(Part):
     def prepare(self, device) -> None:
         pass
 
-    def place(self, qkv, heads: HeadShape, step, line, append: bool = True) -> None:  # pragma: no cover - interface
+    def place(self, qkv, heads: HeadShape, step, line, append: bool = True,
+              prep: Optional[HeadPrep] = None) -> None:  # pragma: no cover - interface
         """Put the positions ``step.tok_pos`` into the queries and keys of ``qkv``
         ([tokens, heads.width], in place) and, with ``append``, write the keys and values of the
-        rows whose slot is not negative to the cache line (``line.writes`` permitting)."""
+        rows whose slot is not negative to the cache line (``line.writes`` permitting).  ``prep``: what the mixer
+        wants done to the rows first (a bias, head norms); a part that does not know it may refuse a mixer that
+        passes one.  ``heads.n_kv_heads`` is 0 for rows that hold queries only."""
         raise NotImplementedError
 
     def project_and_place(self, x, w_qkv, heads: HeadShape, step, line):

@@ -6,6 +6,10 @@ is added:  x += post(mixer(pre(x)));  x += post(ff(pre(x))).
 ``prenorm``: x += m mixer(pre(x));  x += m ff(pre(x)), with a constant m (``residual_mult``, 1 unless given) and a
 feed-forward that a layer may lack.
 
+``postnorm``: x += norm(mixer(x));  x += norm(ff(x)): the sublayers read the stream itself and only what they give
+is normed (a layer norm here; any norm unfused).  A mixer's ``out_bias`` and the mean of a ``parallel`` mixer's
+branches are formed inside the kernel that norms and adds.
+
 The residual stream is float32 in both precisions.  When the norms are RMSNorm the
 post-norm, the add and the next pre-norm run as one kernel; that also holds across the
 border of two layers: ``forward`` may be handed its input already normed (``normed``) and
@@ -19,7 +23,8 @@ import torch
 
 from ..kernels import ops
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block
-from .norm import RMSNorm
+from .norm import LayerNorm, NoNorm, RMSNorm
+from .parallel import ParallelMixer
 from .spec import LayerSpec, PartSpec
 
 
@@ -141,3 +146,58 @@ class PreNormBlock(_LayerParts):
         if next_norm is not None:
             return resid, n
         return resid
+
+
+@BLOCKS.register("postnorm")
+class PostNormBlock(_LayerParts):
+    """x += norm(mixer(x)); x += norm(ff(x)).  What a sublayer reads is the stream in the activations' element type:
+    the kernel that adds a sublayer's normed output writes that copy too (and hands it to the next layer when that
+    one also reads the stream as it is)."""
+
+    NORM_NAMES = ("post_mixer", "post_ff")
+
+    def __init__(self, layer: LayerSpec):
+        super().__init__(layer)
+        self._reads = NoNorm(PartSpec("none", {}))
+        if hasattr(self.mixer, "defer_out_bias"):           # the output's bias rides in the kernel that norms and adds
+            self.mixer.defer_out_bias = True
+
+    def first_norm(self):
+        return self._reads
+
+    def _add(self, resid: torch.Tensor, y, norm, act, want_copy: bool, bias=None, branches=None):
+        """resid += norm(y); returns the new stream as activations when ``want_copy``."""
+        copy = act if want_copy else None
+        if isinstance(norm, LayerNorm):
+            if branches is not None:
+                mixer, outs = branches
+                return ops.add_mean_layernorm(resid, outs, mixer.out_weights, mixer.eps, norm.weight, norm.eps, copy)
+            return norm.add_to(resid, y, bias=bias, copy_dtype=copy)
+        if branches is not None:
+            mixer, outs = branches
+            y = ops.mean_rmsnorm(outs, mixer.out_weights, mixer.eps, act)
+        if bias is not None:
+            y = ops.add_bias_(y, bias)
+        ops.add_(resid, norm(y, act))
+        return ops.cast(resid, act) if want_copy else None
+
+    def forward(self, resid: torch.Tensor, step, line, normed=None, next_norm=None):
+        act = step.act_dtype
+        nm = self.norms
+        n = normed if normed is not None else ops.cast(resid, act)
+        handed = isinstance(next_norm, NoNorm)
+        last_is_mixer = self.ff is None
+        want = (not last_is_mixer) or handed
+        if isinstance(self.mixer, ParallelMixer) and isinstance(nm["post_mixer"], LayerNorm):
+            outs = self.mixer.forward_branches(n, step, line)
+            n = self._add(resid, None, nm["post_mixer"], act, want, branches=(self.mixer, outs))
+        else:
+            y = self.mixer.forward(n, step, line)
+            bias = self.mixer.out_bias if getattr(self.mixer, "defer_out_bias", False) else None
+            n = self._add(resid, y, nm["post_mixer"], act, want, bias=bias)
+        if self.ff is not None:
+            y = self.ff.forward(n, step)
+            n = self._add(resid, y, nm["post_ff"], act, handed)
+        if next_norm is None:
+            return resid
+        return resid, (n if handed else next_norm(resid, act))

@@ -1,4 +1,4 @@
-"""Feed-forward parts.  ``gated_mlp``: down(act(gate(x)) * up(x)).
+"""Feed-forward parts.  ``gated_mlp``: down(act(gate(x)) * up(x)).  ``mlp``: down(act(up(x))), without a gate.
 
 Reference: two products and a GO_GEGLU dispatch, then the down product
 (src/models/QuickNN.Models.Gemma2.pas:184-187; gelu_tanh at shaders/tensor.comp:23).
@@ -48,3 +48,34 @@ class GatedMLP(FeedForward):
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
         h = project(x, self.w_gate_up, epilogue=ops.EPI_GATED, activation=self.activation)
         return project(h, self.w_down)
+
+
+@FEED_FORWARDS.register("mlp")
+class MLP(FeedForward):
+    """down(act(up(x))) with ``activation`` one of ``ops.ACT_CODES`` (``relu2``: the square of relu)."""
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.activation = str(spec.params["activation"])
+        if self.activation not in ops.ACT_CODES:
+            raise ValueError(f"activation {self.activation!r} is not one of {sorted(ops.ACT_CODES)}")
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        H, I = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        M = cls.PARAM_ROLE_MATRIX
+        return {"up_proj": ((I, H), M), "down_proj": ((H, I), M)}
+
+    def load(self, tensors, compute_dtype, device) -> None:
+        self.w_up = tensors["up_proj"].contiguous()
+        self.w_down = tensors["down_proj"].contiguous()
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_up, self.w_down))
+
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        return project(ops.activation(project(x, self.w_up), self.activation), self.w_down)

@@ -1,4 +1,6 @@
-"""Norms.  ``rmsnorm``: y = x / sqrt(mean(x^2) + eps) * (w + offset), offset 1 for the
+"""Norms.  ``layernorm``: y = (x - mean) / sqrt(var + eps) * w, var the mean of the squared deviations, no bias.
+``none``: the rows as they are, in the element type asked for (what a sublayer reads when it reads the stream itself).
+``rmsnorm``: y = x / sqrt(mean(x^2) + eps) * (w + offset), offset 1 for the
 "(1 + w)" flavour.  Reference: GO_NORM without centring and bias
 (src/backends/vulkan/shaders/tensor.comp:63-72; Operations.pas:129-149); the
 reference's files hold 1 + w already (src/models/QuickNN.Models.Gemma2.pas:58), the
@@ -49,3 +51,38 @@ class RMSNorm(Norm):
             return ops.add_rmsnorm(resid, y, self.weight, self.eps, self.unit_offset)
         return ops.add_rmsnorm(resid, y, self.weight, self.eps, self.unit_offset,
                                then.weight, then.eps, then.unit_offset, out_dtype)
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Norm):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.weight: Optional[torch.Tensor] = None
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        return {"weight": ((int(spec.params["size"]),), cls.PARAM_ROLE_SCALE)}
+
+    def load(self, tensors, compute_dtype, device) -> None:
+        self.weight = tensors["weight"].contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        return ops.layernorm(x, self.weight, self.eps, out_dtype)
+
+    def add_to(self, resid: torch.Tensor, y: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               copy_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+        """resid += self(y + bias); with ``copy_dtype`` returns the new stream in that element type, in one kernel."""
+        return ops.add_layernorm(resid, y, self.weight, self.eps, bias, copy_dtype)
+
+
+@NORMS.register("none")
+class NoNorm(Norm):
+    """No norm at all: the rows in the element type asked for."""
+
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        return ops.cast(x, out_dtype)
