@@ -165,7 +165,7 @@ QNN_API int qnn_add_layernorm(float* resid, const void* y, int y_dt, const void*
     if ((size_t)H * sizeof(float) > 160 * 1024) return QNN_ERR_UNSUPPORTED;
     const size_t smem = (size_t)H * sizeof(float);
     static bool set = false;
-    if (smem > 48 * 1024 && !set) {
+    if (smem > 40 * 1024 && !set) {      // beside the static shared memory
         cudaFuncSetAttribute(add_layernorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         set = true;
     }
@@ -184,7 +184,7 @@ QNN_API int qnn_mean_rmsnorm(const void* const* ys, const void* const* ws, int n
     if (int rc = fill(br, ys, ws, n)) return rc;
     const size_t smem = (size_t)H * sizeof(float);
     static bool set = false;
-    if (smem > 48 * 1024 && !set) {
+    if (smem > 40 * 1024 && !set) {      // beside the static shared memory
         cudaFuncSetAttribute(mean_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         set = true;
     }
@@ -202,7 +202,7 @@ QNN_API int qnn_add_mean_layernorm(float* resid, const void* const* ys, const vo
     if (int rc = fill(br, ys, ws, n)) return rc;
     const size_t smem = (size_t)H * sizeof(float);
     static bool set = false;
-    if (smem > 48 * 1024 && !set) {
+    if (smem > 40 * 1024 && !set) {      // beside the static shared memory
         cudaFuncSetAttribute(add_mean_layernorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         set = true;
     }

@@ -106,7 +106,9 @@ def rotate(x: np.ndarray, rot: dict, interleaved: bool, first_position: int = 0)
     if dims == 0:
         return x
     n = x.shape[0]
-    ang = (np.arange(n, dtype=F) + first_position)[:, None] * rotary_frequencies(rot)[None, :]   # [n, dims/2]
+    # the design forms positions and angles in 32-bit: frequency and product are rounded to float32
+    pos = (np.arange(n) + first_position).astype(np.float32)
+    ang = (pos[:, None] * rotary_frequencies(rot).astype(np.float32)[None, :]).astype(F)          # [n, dims/2]
     c, s = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
     out = x.copy()
     if interleaved:
