@@ -261,10 +261,12 @@ def timed_tiny(torch):
 
 # ---- another design beside its closest model at equal size (--design) ------------------------------------
 
-def design_sizes(name):
-    """(Fuposun config, Gemma 2 config) with the same width, depth, vocabulary, window and dense feed-forward width.
-    ``2b``: the 2B layer sizes; ``1b``: about half of them.  Layers come in the pattern latent attention + dense,
-    latent attention + experts, linear attention + dense, latent attention + experts."""
+def design_sizes(name, design="fuposun"):
+    """The configurations that ``--design`` times side by side, the design first: all have the same width, depth,
+    vocabulary, window and dense feed-forward width.  ``2b``: the 2B layer sizes; ``1b``: about half of them.
+    Fuposun's layers come in the pattern latent attention + dense, latent attention + experts, linear attention +
+    dense, latent attention + experts; Tumudra's: windowed attention beside a matrix memory, attention, retention,
+    attention on the keys and values of the attention layer before it (all with the dense feed-forward)."""
     W, ff, heads, hd, kvh, layers, vocab, window = {
         "2b": (2304, 9216, 8, 256, 4, 8, 32768, 4096), "1b": (1536, 6144, 8, 128, 4, 8, 32768, 2048)}[name]
     rank, qr, d = (256, 768, 128) if name == "2b" else (128, 512, 64)
@@ -281,7 +283,27 @@ def design_sizes(name):
     gemma = dict(SIZES, hidden_size=W, intermediate_size=ff, num_attention_heads=heads, num_key_value_heads=kvh,
                  head_dim=hd, num_hidden_layers=layers, vocab_size=vocab, sliding_window=window,
                  query_pre_attn_scalar=hd)
-    return fupo, gemma
+    if design == "fuposun":
+        return [("fuposun", fupo), ("gemma2", gemma)]
+    mh = W // (2 * d)                                          # memory heads: the linear-attention layer's sizes
+    att = {"heads": heads, "kv_heads": kvh, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "rot": {"base": 1e4, "dims": hd}}
+    left = dict(att, mask={"size": window},
+                rot={"base": 1e4, "dims": hd // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+    tlayers = []
+    for i in range(layers):
+        kind = i % 4
+        if kind == 0:
+            mixer = ("parallel", {"left": left, "right": {"heads": mh, "dim": d, "vdim": 2 * d, "gate_cap": 15.0}})
+        elif kind == 1:
+            mixer = ("attention", att)
+        elif kind == 2:
+            mixer = ("retention", {"heads": mh, "dim": d, "vdim": 2 * d, "rot": {"base": 1e4, "dims": d},
+                                   "decay": [1.0 - 2.0 ** -(5 + h % 8) for h in range(mh)]})
+        else:
+            mixer = ("attention", dict(att, kv_from=i - 2))
+        tlayers.append({"type": mixer[0], "mixer": mixer[1], "mlp": dense})
+    tumu = dict(architecture="Tumudra", vocab=vocab, width=W, embedding={"scale": 1.0}, norm={"eps": 1e-6}, layers=tlayers)
+    return [("tumudra", tumu), ("fuposun", fupo), ("gemma2", gemma)]
 
 
 def design_run(args, torch, pk):
@@ -292,7 +314,7 @@ def design_run(args, torch, pk):
            "prefill_tokens": PREFILL_TOKENS, "sizes": {}}
     for size in args.design_sizes.split(","):
         out["sizes"][size] = {}
-        for which, cfg in zip((args.design, "gemma2"), design_sizes(size)):
+        for which, cfg in design_sizes(size, args.design):
             vocab = cfg.get("vocab", cfg.get("vocab_size"))
             llm = LLM.random(cfg, SEED, dtype="bfloat16", max_context=args.context, max_batch=args.batch,
                              max_tokens=args.batch * args.context)
@@ -360,8 +382,9 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-baseline", action="store_true", help="do not time the plain PyTorch / NumPy baselines")
-    ap.add_argument("--design", default=None, choices=["fuposun"],
-                    help="instead of the record: this design beside Gemma 2 at equal size (prefill, decode, kernels)")
+    ap.add_argument("--design", default=None, choices=["fuposun", "tumudra"],
+                    help="instead of the record: this design beside the library's other models at equal size "
+                         "(prefill, decode, kernels)")
     ap.add_argument("--design-sizes", default="1b,2b", help="with --design: which of 1b, 2b")
     args = ap.parse_args()
 

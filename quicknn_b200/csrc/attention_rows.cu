@@ -249,29 +249,34 @@ __global__ void extend_gather_kernel(const bf16* __restrict__ qkv, const bf16* _
                                      int page_size, int ring, const int* __restrict__ slots,
                                      const int* __restrict__ seq_start, const int* __restrict__ seq_row0,
                                      const int* __restrict__ seq_len, const int* __restrict__ whole_row0,
-                                     bf16* __restrict__ whole, int nq, int nkv, int hd) {
+                                     bf16* __restrict__ whole, int nq, int nkv, int hd, int queries_only) {
     pdl_wait();
     const int p = blockIdx.x, b = blockIdx.y;
-    const int start = seq_start[b], n = seq_len[b];
+    const int start = seq_start != nullptr ? seq_start[b] : 0, n = seq_len[b];
     if (p >= start + n) return;
     const int width = (nq + 2 * nkv) * hd, chunks = width / 8;
     uint4* dst = reinterpret_cast<uint4*>(whole + ((size_t)whole_row0[b] + p) * width);
-    if (p >= start) {
-        const uint4* src = reinterpret_cast<const uint4*>(qkv + ((size_t)seq_row0[b] + (p - start)) * width);
-        for (int c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = src[c];
-        return;
+    const int qc = nq * hd / 8, hc = hd / 8, kvc = nkv * hc;
+    const bool fresh = p >= start;                    // a row of this step
+    if (fresh) {
+        // the step's own projections: the whole row, or (queries_only: rows of a layer that reads another layer's
+        // cache line) the queries alone, the keys and values of every position coming from the cache below
+        const int src_chunks = queries_only ? qc : chunks;
+        const uint4* src = reinterpret_cast<const uint4*>(qkv + ((size_t)seq_row0[b] + (p - start)) * (src_chunks * 8));
+        for (int c = threadIdx.x; c < src_chunks; c += blockDim.x) dst[c] = src[c];
+        if (!queries_only) return;
     }
     const int slot = slots[b];
-    const bool held = slot >= 0 && (ring <= 0 || p >= start - ring);
+    const int last = queries_only ? start + n : start;        // positions below `last` are in the cache
+    const bool held = slot >= 0 && (ring <= 0 || p >= last - ring);
     const int r = ring > 0 ? p % ring : p;
     size_t base = 0;
     if (held) {
         const int page = page_table[(size_t)slot * max_pages + r / page_size];
         base = ((size_t)page * nkv * page_size + (r % page_size)) * hd;
     }
-    const int qc = nq * hd / 8, hc = hd / 8, kvc = nkv * hc;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    for (int c = threadIdx.x + (fresh ? qc : 0); c < chunks; c += blockDim.x) {
         uint4 v = zero;
         if (held && c >= qc) {
             const int e = c - qc;
@@ -284,15 +289,17 @@ __global__ void extend_gather_kernel(const bf16* __restrict__ qkv, const bf16* _
     }
 }
 
+// queries_only: qkv holds [rows, nq * hd] queries; keys and values of the step's own positions are in the cache already
+// (another layer appended them earlier in the step).  seq_start may be null: every sequence starts at position 0.
 QNN_API int qnn_attn_extend_gather(const void* qkv, const void* k_pool, const void* v_pool, const int* page_table,
                                    int max_pages, int page_size, int ring, const int* slots, const int* seq_start,
                                    const int* seq_row0, const int* seq_len, const int* whole_row0, void* whole, int B,
-                                   int longest, int nq, int nkv, int hd, cudaStream_t st) {
+                                   int longest, int nq, int nkv, int hd, int queries_only, cudaStream_t st) {
     if (B <= 0 || longest <= 0) return 0;
     if (hd <= 0 || (hd & 7) || page_size <= 0 || B > 65535) return QNN_ERR_UNSUPPORTED;
     if ((((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)whole) & 15)) return QNN_ERR_ARGUMENT;
     qnn::launch_pdl(extend_gather_kernel, dim3((unsigned)longest, (unsigned)B), dim3(128), 0, st, (const bf16*)qkv,
                     (const bf16*)k_pool, (const bf16*)v_pool, page_table, max_pages, page_size, ring, slots, seq_start,
-                    seq_row0, seq_len, whole_row0, (bf16*)whole, nq, nkv, hd);
+                    seq_row0, seq_len, whole_row0, (bf16*)whole, nq, nkv, hd, queries_only);
     QNN_LAUNCH_CHECK();
 }

@@ -140,6 +140,9 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 #define QNN_ACT_GELU_TANH 0
 #define QNN_ACT_SILU 1
 #define QNN_ACT_RELU2 2          // the square of relu
+// A product without a gate whose epilogue is an activation gets the activation's code plus this as its `act`
+// argument (with the epilogue code "none"): act(x W^T).  Codes below it mean what they meant.
+#define QNN_ACT_ALONE 16
 __device__ __forceinline__ float relu2(float x) { const float r = fmaxf(x, 0.f); return x == x ? r * r : x; }
 __device__ __forceinline__ float activate(float x, int act) {
     return act == QNN_ACT_SILU ? silu(x) : (act == QNN_ACT_RELU2 ? relu2(x) : gelu_tanh(x));

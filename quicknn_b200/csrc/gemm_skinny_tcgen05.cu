@@ -289,7 +289,8 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
                 } else if (EPI == EPI_SOFTCAP) {
                     reinterpret_cast<float*>(C)[(size_t)m * Nout + n] = softcap(a4[j], cap);
                 } else {
-                    reinterpret_cast<bf16*>(C)[(size_t)m * Nout + n] = __float2bfloat16_rn(a4[j]);
+                    const float r = act >= QNN_ACT_ALONE ? activate_fast(a4[j], act - QNN_ACT_ALONE) : a4[j];
+                    reinterpret_cast<bf16*>(C)[(size_t)m * Nout + n] = __float2bfloat16_rn(r);
                 }
             }
         }

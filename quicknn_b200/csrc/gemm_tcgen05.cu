@@ -197,6 +197,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                    if (act >= QNN_ACT_ALONE) {              // an activation without a gate: act(A B^T)
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = activate_fast(f[j], act - QNN_ACT_ALONE);
+                    }
                 }
                 if (c0 + 32 >= OUT_COLS) {
                     // the last columns are in registers: hand the accumulator back before storing them

@@ -223,6 +223,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                            if (act >= QNN_ACT_ALONE) {      // an activation without a gate: act(A B^T)
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) f[j] = activate_fast(f[j], act - QNN_ACT_ALONE);
+                            }
                         }
                         if (c0 + 32 >= OUT_COLS) {
                             // the last columns are in registers: hand the accumulator back to the leader
@@ -267,6 +271,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                    if (act >= QNN_ACT_ALONE) {              // an activation without a gate: act(A B^T)
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = activate_fast(f[j], act - QNN_ACT_ALONE);
+                    }
                 }
                 if (c0 + 32 >= OUT_COLS) {
                     // the last columns are in registers: hand the accumulator back to the leader before storing them

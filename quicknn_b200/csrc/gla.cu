@@ -270,9 +270,8 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, long long ldo
 // ---- gates of a matrix memory with a running maximum ---------------------------------------------------------------
 // pre: float32 [rows, ldp] with the input gate's pre-activation of head h at column h and the forget gate's at H + h;
 // bias: [2H] (input gates, then forget gates).  i = cap tanh((pre_i + b_i) / cap); f = log sigmoid(cap tanh((pre_f +
-// b_f) / cap)).  m_t = max(f_t + m_{t-1}, i_t) is a linear recurrence over (max, +): a row is the map m -> max(m + a, b)
-// with (a, b) = (f, i), and two rows in a row compose to (a1 + a2, max(b1 + a2, b2)), so a warp scans 32 rows at a time
-// with shuffles.  gates: float32 [rows, 3H]: the decay exp(f_t + m_{t-1} - m_t), the key weight exp(i_t - m_t),
+// b_f) / cap)).  A warp takes 32 rows at a time: every lane forms one row's log gates (the hyperbolic tangents, the
+// logarithm), then all lanes walk m_t = max(f_t + m_{t-1}, i_t) through the 32 rows in order.  gates: float32 [rows, 3H]: the decay exp(f_t + m_{t-1} - m_t), the key weight exp(i_t - m_t),
 // exp(-m_t).  A warp per (sequence, head); m of the slot's head at mstate[slot * state_stride + h].
 __global__ void mlstm_gates_kernel(const float* __restrict__ pre, long long ldp, const void* __restrict__ bias, int b_dt,
                                    float cap, const int* __restrict__ seq_row0, const int* __restrict__ seq_len,
@@ -296,18 +295,19 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ pre, long long ldp,
             const float c = cap * tanhf(zf / cap);
             gf = fminf(c, 0.f) - log1pf(expf(-fabsf(c)));
         }
-        float a = gf, bb = gi;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const float pa = __shfl_up_sync(0xffffffffu, a, off), pb = __shfl_up_sync(0xffffffffu, bb, off);
-            if (lane >= off) {
-                bb = fmaxf(pb + a, bb);
-                a = pa + a;
+        // the rows of the chunk in order; every lane walks them all, so m is the same bit for bit whether a row came
+        // in a prompt, in a portion or alone
+        float before = m, mt = m;
+#pragma unroll 8
+        for (int j = 0; j < 32; ++j) {
+            const float fj = __shfl_sync(0xffffffffu, gf, j), ij = __shfl_sync(0xffffffffu, gi, j);
+            const float next = fmaxf(m + fj, ij);
+            if (lane == j) {
+                before = m;
+                mt = next;
             }
+            m = next;
         }
-        const float mt = fmaxf(m + a, bb);
-        float before = __shfl_up_sync(0xffffffffu, mt, 1);
-        if (lane == 0) before = m;
         if (t < n) {
             float* gr = gates + (size_t)(row0 + t) * ldg;
             const bool live = slot >= 0;
@@ -315,7 +315,6 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ pre, long long ldp,
             gr[H + h] = live ? expf(gi - mt) : 0.f;
             gr[2 * H + h] = live ? expf(-mt) : 1.f;
         }
-        m = __shfl_sync(0xffffffffu, mt, 31);
     }
     if (slot >= 0 && lane == 0) mstate[(size_t)slot * state_stride + h] = m;
 }

@@ -306,6 +306,8 @@ __global__ void __launch_bounds__(NW * 32, skinny_min_blocks<NT, NW>()) skinny_b
             v = activate_fast(v, act) * u;          // bfloat16 inputs and output: the fast activation
         } else if (EPI == EPI_SOFTCAP || EPI == EPI_ARGMAX) {
             v = softcap(v, cap);
+        } else if (EPI == EPI_NONE && act >= QNN_ACT_ALONE) {
+            v = activate_fast(v, act - QNN_ACT_ALONE);       // an activation without a gate
         }
         if constexpr (EPI == EPI_ARGMAX) {
             // the 16 lanes of a half-warp hold the CTA's 16 columns of row m: the largest wins, the lowest

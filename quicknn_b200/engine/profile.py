@@ -187,7 +187,7 @@ class OpTimer:
 
     SKIP = {"status_words", "finite_flag", "raise_on_status", "check_gemm_status", "wait_status_message", "dt_code",
             "attention_refusal", "linear_refusal", "sample_scratch_bytes", "head_candidates", "head_argmax_fusable",
-            "qkv_rope_cache_fusable", "cache_append", "gemm_tcgen05", "gemm_skinny_tcgen05"}
+            "qkv_rope_cache_fusable", "cache_append", "gemm_tcgen05", "gemm_skinny_tcgen05", "activation_"}
 
     def __init__(self, engine, hbm_gbs: float, tflops: float, context: int = 0):
         self.engine, self.hbm, self.tflops, self.context = engine, hbm_gbs * 1e9, tflops * 1e12, context
@@ -223,6 +223,22 @@ class OpTimer:
             flops = 4.0 * T * H * dim * vdim
             byts = float(T * (2 * H * dim + H * vdim) * proj.element_size() + T * H * dim * 4 + T * H * vdim * 4
                          + 2 * n_seqs * H * dim * vdim * 4)
+        elif name == "memory_scan":
+            proj, normaliser, n_seqs, H, dim, vdim = a[0], a[9], a[14], a[15], a[16], a[17]
+            T, vs = proj.shape[0], vdim + (1 if normaliser else 0)
+            flops = 4.0 * T * H * dim * vs
+            byts = float(T * (2 * H * dim + H * vdim) * proj.element_size() + T * H * vs * 4 + 2 * n_seqs * H * dim * vs * 4)
+        elif name == "attn_prefill_paged":
+            qkv, nq, nkv, hd, window = a[0], a[1], a[2], a[3], a[13]
+            T = qkv.shape[0]
+            keys = sum(min(p + 1, window) if window else p + 1 for p in range(T))
+            flops = 4.0 * nq * hd * keys
+            byts = float(T * nq * hd * qkv.element_size() * 2 + 2 * T * nkv * hd * qkv.element_size())
+        elif name == "head_prep":
+            src, nq, nk, nv, hd = a[0], a[2], a[3], a[4], a[5]
+            dst = kw.get("dst")
+            width = (nq + nk) * hd + nv
+            byts = float(src.shape[0] * width * (src.element_size() + (dst.element_size() if dst is not None else src.element_size())))
         elif name == "moe_experts":
             x, top, wgu, wd = a[0], a[3], a[4], a[5]
             T, W = x.shape

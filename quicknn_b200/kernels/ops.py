@@ -22,6 +22,8 @@ from . import lib as _lib
 
 F32, BF16 = 0, 1
 EPI_NONE, EPI_SOFTCAP, EPI_GATED = 0, 1, 2
+EPI_ACT = 5                  # act(x w^T) without a gate; the launchers get it as epilogue "none" with the code below
+ACT_ALONE = 16               # added to an activation's code: the product's epilogue applies it to the plain product
 ACT_CODES = {"gelu_tanh": 0, "silu": 1, "relu2": 2}
 SKINNY_MAX_ROWS = 64
 
@@ -340,8 +342,11 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, 
     _req(w, "w", torch.bfloat16, 2)
     M, K = x.shape
     N = w.shape[0]
-    if epilogue not in (EPI_NONE, EPI_GATED) or K % 8 or w.shape[1] != K:
+    if epilogue not in (EPI_NONE, EPI_GATED, EPI_ACT) or K % 8 or w.shape[1] != K:
         return None
+    act_code = ACT_CODES[activation] + (ACT_ALONE if epilogue == EPI_ACT else 0)
+    if epilogue == EPI_ACT:
+        epilogue = EPI_NONE
     n_out = N // 2 if epilogue == EPI_GATED else N
     if out is None:
         out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
@@ -353,12 +358,12 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, 
     if pair is None:
         pair = GEMM_2CTA and M > 128
     if pair:
-        code = L.qnn_gemm_tcgen05_2cta(_p(x), _p(w), _p(out), M, N, K, epilogue, ACT_CODES[activation],
+        code = L.qnn_gemm_tcgen05_2cta(_p(x), _p(w), _p(out), M, N, K, epilogue, act_code,
                                        _p(_status_word(x.device)), _stream())
         if code != _lib.ERR_UNSUPPORTED:
             _lib.check(code, "gemm_tcgen05_2cta")
             return out
-    code = L.qnn_gemm_tcgen05(_p(x), _p(w), _p(out), M, N, K, epilogue, ACT_CODES[activation],
+    code = L.qnn_gemm_tcgen05(_p(x), _p(w), _p(out), M, N, K, epilogue, act_code,
                               _p(_status_word(x.device)), _stream())
     if code == _lib.ERR_UNSUPPORTED:
         return None
@@ -377,6 +382,9 @@ def gemm_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI
     N = w.shape[0]
     if M > 128 or K % 8 or w.shape[1] != K:
         return None
+    act_code = ACT_CODES[activation] + (ACT_ALONE if epilogue == EPI_ACT else 0)
+    if epilogue == EPI_ACT:
+        epilogue = EPI_NONE
     n_out = N // 2 if epilogue == EPI_GATED else N
     out_dtype = torch.float32 if epilogue == EPI_SOFTCAP else torch.bfloat16
     if out is None:
@@ -387,7 +395,7 @@ def gemm_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI
             raise ValueError(f"gemm_skinny_tcgen05: out is {tuple(out.shape)}, the product [{M}, {n_out}]")
     L = _lib.load()
     code = L.qnn_gemm_skinny_tcgen05(_p(x), _p(w), _p(out), M, N, K, epilogue, float(cap or 0.0),
-                                     ACT_CODES[activation], _p(_status_word(x.device)), _stream())
+                                     act_code, _p(_status_word(x.device)), _stream())
     if code == _lib.ERR_UNSUPPORTED:
         return None
     _lib.check(code, "gemm_skinny_tcgen05")
@@ -461,9 +469,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
     n_out = N // 2 if epilogue == EPI_GATED else N
     if out_dtype is None:
         out_dtype = torch.float32 if epilogue == EPI_SOFTCAP else x.dtype
+    if epilogue == EPI_ACT and (x.dtype == torch.float32 or K % 8 or not USE_TCGEN05 or out_dtype != torch.bfloat16):
+        # act(x w^T) where the product's kernels have no such epilogue: the product, then the activation
+        return activation_(linear(x, w, out_dtype=out_dtype), activation)
     L = _lib.load()
     capv = float(cap or 0.0)
-    act = ACT_CODES[activation]
+    act = ACT_CODES[activation] + (ACT_ALONE if epilogue == EPI_ACT else 0)
+    fused_act = epilogue == EPI_ACT
+    if fused_act:
+        epilogue = EPI_NONE               # the bfloat16 kernels below read the activation from `act`
     if x.dtype == torch.float32:
         if out_dtype != torch.float32:
             raise TypeError("float32 products give float32")
@@ -483,8 +497,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
         _lib.check(L.qnn_linear_bf16_any(_p(x), _p(w), _p(out), dt_code(out), M, N, K, epilogue, capv, act, _stream()),
                    "linear_bf16_any")
         return out
+    kind = EPI_ACT if fused_act else epilogue          # what the tcgen05 wrappers are asked for
     if _takes_skinny_tcgen05(M, N, K) and out_dtype == (torch.float32 if epilogue == EPI_SOFTCAP else torch.bfloat16):
-        y = gemm_skinny_tcgen05(x, w, epilogue=epilogue, cap=cap, activation=activation)
+        y = gemm_skinny_tcgen05(x, w, epilogue=kind, cap=cap, activation=activation)
         if y is not None:
             return y
     def small(xr: torch.Tensor, out: torch.Tensor) -> None:
@@ -502,12 +517,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
                 # the last rows would open one more round of 256 x 256 tiles: they go to the kernel for few rows
                 head = M - tail
                 out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
-                ok = (gemm_tcgen05(x[:head], w, epilogue=epilogue, activation=activation, out=out[:head]) is not None
-                      and gemm_skinny_tcgen05(x[head:], w, epilogue=epilogue, activation=activation,
+                ok = (gemm_tcgen05(x[:head], w, epilogue=kind, activation=activation, out=out[:head]) is not None
+                      and gemm_skinny_tcgen05(x[head:], w, epilogue=kind, activation=activation,
                                               out=out[head:]) is not None)
                 if ok:
                     return out
-            y = gemm_tcgen05(x, w, epilogue=epilogue, activation=activation)
+            y = gemm_tcgen05(x, w, epilogue=kind, activation=activation)
             if y is not None:
                 return y
         elif epilogue == EPI_SOFTCAP:          # logits wanted at many places: the product, then the cap in float32
@@ -617,6 +632,40 @@ def attn_prefill_paged(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int
     return out
 
 
+def attn_shared_tensor_core(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor,
+                            v_pool: torch.Tensor, page_table: torch.Tensor, page_size: int, ring: int, slots: torch.Tensor,
+                            seq_row0: torch.Tensor, seq_len: torch.Tensor, scale: float, cap: Optional[float],
+                            window: Optional[int], longest: int, whole=None) -> Optional[torch.Tensor]:
+    """Attention of query rows ``q`` ([rows, n_heads * head_dim]) whose keys and values, this step's positions included,
+    are in the paged cache already (a layer that reads the line another layer wrote earlier in the step), on the
+    tensor-core prompt kernel: keys and values are copied out of the pages beside the queries into whole sequences,
+    as ``attn_extend`` does.  ``whole``: the sequences with their cached tokens in front when the step continues
+    sequences; None for whole prompts.  Returns None where that kernel does not serve (the caller takes the generic one)."""
+    if not (ATTN_TCGEN05 and q.dtype == torch.bfloat16 and head_dim in (64, 128, 256)):
+        return None
+    _req(q, "q", torch.bfloat16, 2)
+    L = _lib.load()
+    width = (n_heads + 2 * n_kv) * head_dim
+    if whole is None:
+        B, total, most = seq_row0.numel(), q.shape[0], int(longest)
+        start, row0, length, new_row0, new_len = None, seq_row0, seq_len, seq_row0, seq_len
+    else:
+        B, total, most = whole.row0.numel(), whole.total, whole.longest
+        start, row0, length, new_row0, new_len = whole.start, whole.row0, whole.length, whole.new_row0, whole.new_len
+    rows = torch.empty((total, width), dtype=q.dtype, device=q.device)
+    _lib.check(L.qnn_attn_extend_gather(
+        _p(q), _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1], page_size, ring, _p(slots), _p(start),
+        _p(new_row0), _p(new_len), _p(row0), _p(rows), B, most, n_heads, n_kv, head_dim, 1, _stream()), "attn_extend_gather")
+    out_rows = torch.empty((total, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    code = L.qnn_attn_prefill_tcgen05(
+        _p(rows), total, _p(out_rows), out_rows.shape[1], _p(row0), _p(length), _p(start), B, most, n_heads, n_kv,
+        head_dim, float(scale), float(cap or 0.0), int(window or 0), _p(_status_word(q.device)), _stream())
+    if code == _lib.ERR_UNSUPPORTED:
+        return None
+    _lib.check(code, "attn_prefill_tcgen05")
+    return out_rows if whole is None else gather_rows(out_rows, whole.tok_row, q.dtype)
+
+
 def attn_extend(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
                 page_table: torch.Tensor, page_size: int, ring: int, tok_pos: torch.Tensor, tok_row0: torch.Tensor,
                 tok_slot: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int], whole=None):
@@ -644,7 +693,7 @@ def attn_extend(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_poo
         _lib.check(L.qnn_attn_extend_gather(
             _p(qkv), _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1], page_size, ring, _p(whole.slots),
             _p(whole.start), _p(whole.new_row0), _p(whole.new_len), _p(whole.row0), _p(rows), B, whole.longest,
-            n_heads, n_kv, head_dim, _stream()), "attn_extend_gather")
+            n_heads, n_kv, head_dim, 0, _stream()), "attn_extend_gather")
         out_rows = torch.empty((whole.total, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
         code = L.qnn_attn_prefill_tcgen05(
             _p(rows), whole.total, _p(out_rows), out_rows.shape[1], _p(whole.row0), _p(whole.length), _p(whole.start), B,
@@ -1152,6 +1201,13 @@ def add_bias_(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
     _lib.check(_lib.load().qnn_add_bias(_p(y), dt_code(y), _p(bias), dt_code(bias), y.shape[0], y.shape[1], _stream()),
                "add_bias")
     return y
+
+
+def activation_(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """x = act(x) elementwise, in place."""
+    _req(x, "x")
+    _lib.check(_lib.load().qnn_activation(_p(x), dt_code(x), _p(x), ACT_CODES[kind], x.numel(), _stream()), "activation")
+    return x
 
 
 def activation(x: torch.Tensor, kind: str) -> torch.Tensor:

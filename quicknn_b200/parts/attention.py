@@ -232,9 +232,18 @@ class AttentionMixer(Mixer):
             if line.ring and step.max_q_len > room:
                 raise ValueError(f"a step of {step.max_q_len} tokens overruns the ring of {line.ring} "
                                  f"positions that this layer reads from another layer's cache line")
-            a = ops.attn_prefill_paged(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v,
-                                       line.page_table, line.page_size, line.ring, step.tok_pos, step.tok_slot,
-                                       self.scale, self.softcap, self.window)
+            a = None
+            whole = getattr(step, "whole", None) if extend else None
+            if qkv.shape[1] == self.n_heads * self.head_dim and step.seq_row0 is not None and (whole is not None or not extend):
+                # queries only, every key in the cache: whole sequences for the tensor-core prompt kernel
+                a = ops.attn_shared_tensor_core(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v,
+                                                line.page_table, line.page_size, line.ring, step.slots, step.seq_row0,
+                                                step.seq_len, self.scale, self.softcap, self.window, step.max_q_len,
+                                                whole=whole)
+            if a is None:
+                a = ops.attn_prefill_paged(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v,
+                                           line.page_table, line.page_size, line.ring, step.tok_pos, step.tok_slot,
+                                           self.scale, self.softcap, self.window)
         elif step.mode == "prefill":
             a = ops.attn_prefill(qkv, self.n_heads, self.n_kv, self.head_dim, step.tok_pos, step.tok_row0,
                                  self.scale, self.softcap, self.window, step.seq_row0, step.seq_len, step.max_q_len)

@@ -78,4 +78,4 @@ class MLP(FeedForward):
         return sum(w.numel() * w.element_size() for w in (self.w_up, self.w_down))
 
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
-        return project(ops.activation(project(x, self.w_up), self.activation), self.w_down)
+        return project(project(x, self.w_up, epilogue=ops.EPI_ACT, activation=self.activation), self.w_down)
