@@ -100,6 +100,117 @@ __global__ void head_prep_kernel(const T* src, long long lds, void* dst, int dst
     }
 }
 
+// The same with 16-byte accesses: a lane holds eight consecutive columns of a head (heads of up to 256 columns, a
+// multiple of 8).  The pair of an interleaved rotation lies inside a lane; the partner of a half-split pair lies
+// rot/16 lanes away and comes by shuffle.  Element types are read at run time (rows and pools of bfloat16 or float32).
+__global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, void* dst, int d_dt, long long ldd, int nq,
+                                     int nk, int nv, int hd, int norm_dim, int rot, int interleaved,
+                                     const void* __restrict__ bias, int b_dt, const void* __restrict__ wq,
+                                     const void* __restrict__ wk, int w_dt, float eps, const float* __restrict__ inv_freq,
+                                     const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, void* k_pool,
+                                     void* v_pool, const int* __restrict__ page_table, int max_pages, int page_size,
+                                     int ring, const int* __restrict__ slot_len, int write_cache) {
+    extern __shared__ float sm[];                   // [rot/2] (cos, sin) pairs
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = tok_pos != nullptr ? tok_pos[t] : 0;
+    const int slot = tok_slot != nullptr ? tok_slot[t] : -1;
+    const int rh = rot / 2;
+    float2* angles = reinterpret_cast<float2*>(sm);
+    for (int j = threadIdx.x; j < rh; j += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[j], &sn, &cs);
+        angles[j] = make_float2(cs, sn);
+    }
+    __syncthreads();
+    size_t cache_base = 0;
+    bool wr = write_cache && slot >= 0;
+    if (wr && ring > 0 && pos + ring < slot_len[slot]) wr = false;
+    if (wr) {
+        const int r = ring > 0 ? pos % ring : pos;
+        const int page = page_table[(size_t)slot * max_pages + r / page_size];
+        cache_base = ((size_t)page * nk * page_size + (r % page_size)) * hd;
+    }
+    const size_t head_stride = (size_t)page_size * hd;
+    const size_t in_row = (size_t)t * lds, out_row = (size_t)t * ldd;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    const int col = lane * 8, shift = rh / 8;
+    const bool active = col < hd;
+    for (int h = warp; h < nq + nk; h += nwarp) {
+        const bool is_k = h >= nq;
+        const size_t c0 = (size_t)h * hd;
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (active) {
+            load8_as_f(src, s_dt, in_row + c0 + col, v);
+            if (bias != nullptr) {
+                float b[8];
+                load8_as_f(bias, b_dt, c0 + col, b);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += b[e];
+            }
+        }
+        const void* w = is_k ? wk : wq;
+        if (w != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (col + e < norm_dim) ss += v[e] * v[e];
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)norm_dim + eps);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (col + e < norm_dim) v[e] = v[e] * inv * load_as_f(w, w_dt, col + e);
+        }
+        if (rot > 0) {
+            if (interleaved) {
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    if (col + e < rot) {
+                        const float2 cs = angles[(col + e) >> 1];
+                        const float a = v[e], b = v[e + 1];
+                        v[e] = a * cs.x - b * cs.y;
+                        v[e + 1] = b * cs.x + a * cs.y;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float above = __shfl_down_sync(0xffffffffu, v[e], shift);     // column c + rot/2
+                    const float below = __shfl_up_sync(0xffffffffu, v[e], shift);       // column c - rot/2
+                    const int c = col + e;
+                    if (c < rh) {
+                        const float2 cs = angles[c];
+                        v[e] = v[e] * cs.x - above * cs.y;
+                    } else if (c < rot) {
+                        const float2 cs = angles[c - rh];
+                        v[e] = v[e] * cs.x + below * cs.y;
+                    }
+                }
+            }
+        }
+        if (active) {
+            store8_from_f(dst, d_dt, out_row + c0 + col, v);
+            if (is_k && wr) store8_from_f(k_pool, d_dt, cache_base + (size_t)(h - nq) * head_stride + col, v);
+        }
+    }
+    const size_t v0 = (size_t)(nq + nk) * hd;
+    const bool v_cache = wr && v_pool != nullptr;
+    if (nv > 0 && (bias != nullptr || v_cache || src != (const void*)dst)) {
+        for (int c = threadIdx.x * 8; c < nv; c += blockDim.x * 8) {
+            float v[8];
+            load8_as_f(src, s_dt, in_row + v0 + c, v);
+            if (bias != nullptr) {
+                float b[8];
+                load8_as_f(bias, b_dt, v0 + c, b);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += b[e];
+            }
+            store8_from_f(dst, d_dt, out_row + v0 + c, v);
+            if (v_cache) store8_from_f(v_pool, d_dt, cache_base + (size_t)(c / hd) * head_stride + (c % hd), v);
+        }
+    }
+}
+
 }  // namespace
 
 // src: [T, lds] rows of `dtype` holding nq query heads, nk key heads (hd columns each) and nv value columns, in that
@@ -122,6 +233,18 @@ QNN_API int qnn_head_prep(const void* src, int dtype, long long lds, void* dst, 
     const int heads = nq + nk;
     int warps = heads >= 8 ? 8 : (heads >= 4 ? 4 : 2);
     if (T > 1024 && warps > 4) warps = 4;
+    // 16-byte accesses where every piece starts on 16 bytes: heads, value columns and row pitches in whole pieces of 8
+    // columns, heads of up to 256, a half-split rotation over a multiple of 16 columns
+    const size_t es = dtype == QNN_DT_BF16 ? 2 : 4, ed = dst_dt == QNN_DT_BF16 ? 2 : 4;
+    const bool aligned = ((uintptr_t)src % 16 == 0) && ((uintptr_t)dst % 16 == 0) && (lds * es) % 16 == 0 &&
+                         (ldd * ed) % 16 == 0 && ((uintptr_t)bias % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) &&
+                         ((uintptr_t)v_pool % 16 == 0);
+    if (aligned && hd % 8 == 0 && hd <= 256 && nv % 8 == 0 && (interleaved ? rot % 2 == 0 : rot % 16 == 0)) {
+        launch_pdl(head_prep_vec_kernel, dim3(T), dim3(warps * 32), (size_t)rot * sizeof(float), st, src, dtype, lds, dst,
+                   dst_dt, ldd, nq, nk, nv, hd, norm_dim, rot, interleaved, bias, b_dt, wq, wk, w_dt, eps, inv_freq, tok_pos,
+                   tok_slot, k_pool, v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache);
+        QNN_LAUNCH_CHECK();
+    }
     const size_t smem = ((size_t)rot + (size_t)warps * hd) * sizeof(float);
     if (smem > 48 * 1024) return QNN_ERR_UNSUPPORTED;
     if (dtype == QNN_DT_BF16)
