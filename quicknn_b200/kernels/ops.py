@@ -1282,6 +1282,24 @@ def head_prep(src: torch.Tensor, col0: int, n_q: int, n_k: int, n_v_cols: int, h
 
 # ---- matrix memories with one decay per head ------------------------------------------------------------------------------
 
+def _segment_rows(longest: int, blocks_per_segment: int, device) -> int:
+    """Rows of a segment when long sequences are walked in segments side by side: ``blocks_per_segment`` blocks run for
+    every segment index (sequences x heads x blocks of value columns), two of them fit an SM, and the walk takes as
+    long as a segment has rows times the rounds of blocks.  So: as many segments as fit the device in one round (of at
+    least 128 rows each, whole chunks of 16 rows); where not even two fit, the standing 256 rows.  Measured at 9 heads
+    of 128 x 257, one prompt of 2048 rows: 8 segments of 256 are 360 blocks, a second round for 64 of them, 0.41 ms;
+    6 segments of 352 are 270 blocks in one round."""
+    key = str(device)
+    if key not in _SM_COUNT:
+        dev = torch.device(device)
+        _SM_COUNT[key] = torch.cuda.get_device_properties(dev).multi_processor_count if dev.type == "cuda" else 148
+    fit = (2 * _SM_COUNT[key]) // max(1, blocks_per_segment)
+    if fit < 2:
+        return GLA_SEGMENT
+    nseg = max(1, min(fit, longest // 128))
+    return max(128, (-(-longest // nseg) + 15) // 16 * 16)
+
+
 def memory_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, decay_ld: int,
                 key_weight: Optional[torch.Tensor], kw_col: int, q_scale: float, normaliser: bool,
                 seq_row0: Optional[torch.Tensor],
@@ -1314,7 +1332,10 @@ def memory_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: t
     seg_len = nseg = 0
     scratch = seg_decay = None
     if seq_row0 is not None and longest >= GLA_SEGMENTS_FROM and n_seqs * -(-longest // GLA_SEGMENT) <= 65535:
-        seg_len, nseg = GLA_SEGMENT, -(-longest // GLA_SEGMENT)
+        seg_len = _segment_rows(longest, n_seqs * n_heads * -(-vs // (64 if dim <= 128 else 32)), proj.device)
+        if n_seqs * -(-longest // seg_len) > 65535:
+            seg_len = GLA_SEGMENT
+        nseg = -(-longest // seg_len)
         scratch = torch.zeros((n_seqs * nseg, n_heads * dim * vs), dtype=torch.float32, device=proj.device)
         seg_decay = torch.empty((n_seqs * nseg, n_heads), dtype=torch.float32, device=proj.device)
     _lib.check(_lib.load().qnn_memory_scan(

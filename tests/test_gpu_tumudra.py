@@ -46,13 +46,16 @@ def f64(w):
     return {k: np.asarray(v, dtype=np.float64) for k, v in w.items()}
 
 
-def near(got, ref, dtype, float32=2e-5):
-    """How whole models are compared.  float32: sharply, by the largest difference (2e-5 of the largest logit; 1e-4 for
-    the configurations drawn at random, where a row now and then sits on a nearly cancelling read-out of a memory).  bfloat16: a layer
-    adds the NORMED output of its sublayers, so what rounding does to a sublayer's output reaches the stream at full
-    size whatever the output's own size was, and the norms per head after a memory keep only the direction of a read-out
-    (at a sequence's first tokens, where the state has rank one, only a sign): a row is compared by the root mean square
-    of its difference against that of the logits, at most a tenth, and one row in thirty (or one) may lie beyond."""
+def near(got, ref, dtype, float32=1e-4):
+    """How whole models are compared.  A layer adds the NORMED output of its sublayers, so an error in a sublayer's output
+    reaches the stream at full size whatever the output's own size was, and the norm per head after a memory keeps only
+    the direction of a read-out: where a query stands almost at a right angle to what the memory holds (one row in a
+    hundred or so, with the queries and keys scaled as they are here), float32 rounding of the read-out becomes 5e-5 of
+    the logits, in the plain order of operations as in any other.  float32: by the largest difference, 1e-4 of the
+    largest logit (3e-4 for the configurations drawn at random, whose gates span up to e^60); a wrong mask, key, window
+    or state moves these models' logits by 1e-2 and more.  bfloat16: a row is compared by the root mean square of its
+    difference against that of the logits, at most a tenth, and one row in thirty (or one) may lie beyond (at a sequence's
+    first tokens the state has rank one and the norm keeps only a sign)."""
     got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
     if dtype == "float32":
         tol = float32 * max(1.0, float(np.abs(ref).max()))
@@ -678,10 +681,7 @@ def test_prompts_in_portions_down_to_two_tokens(tumu, tmp_path, name, dtype, pea
         got = replay.step(entries, end=[f"r{i}" for i in end])
         r = 0
         for i, n in parts:
-            # 1e-4 in float32: one row of model A's prompt (position 77) reads its memory almost at a right angle to
-            # what it holds, and the norm per head that follows turns float32 rounding into 6e-5 of the logits, in a
-            # whole prompt as in portions (the two agree to 6e-6); a wrong mask, key or state moves them by 1e-2 and more
-            ok, err, tol = near(got[r:r + n], ref[i][pos[i]:pos[i] + n], dtype, 1e-4)
+            ok, err, tol = near(got[r:r + n], ref[i][pos[i]:pos[i] + n], dtype)
             assert ok, f"request {i} positions {pos[i]}..{pos[i] + n - 1}: error {err:.3g} > {tol:.3g}"
             pos[i] += n
             r += n
@@ -834,13 +834,13 @@ def test_configurations_drawn_at_random(tmp_path, seed):
         got = eng.step([(s, t[:n]) for s, t, n in zip(slots, reqs, lens)], "all").cpu().numpy()
         at = 0
         for r, n in zip(ref, lens):
-            ok, err, tol = near(got[at:at + n], r[:n], dtype, 1e-4)
+            ok, err, tol = near(got[at:at + n], r[:n], dtype, 3e-4)
             assert ok, f"seed {seed} {dtype}: prompt of {n}: error {err:.3g} > {tol:.3g}  ({raw['layers']})"
             at += n
         for t in range(extra):
             got = eng.step([(s, [q[n + t]]) for s, q, n in zip(slots, reqs, lens)], "last").cpu().numpy()
             for i, (r, n) in enumerate(zip(ref, lens)):
-                ok, err, tol = near(got[i:i + 1], r[n + t:n + t + 1], dtype, 1e-4)
+                ok, err, tol = near(got[i:i + 1], r[n + t:n + t + 1], dtype, 3e-4)
                 assert ok, f"seed {seed} {dtype}: request {i} decoded token {t}: error {err:.3g} > {tol:.3g}"
         for s in slots:
             eng.release(s)
