@@ -777,6 +777,41 @@ def test_the_command_line_serves_the_design(tumu, tmp_path):
     assert ok, (err, tol)
 
 
+def test_layer_sizes_that_take_the_tensor_core_kernels(tmp_path):
+    """Head size 128 (the tcgen05 prompt attention and the tensor-core decode attention, also for the layer on shared keys
+    and values and for values carried wider than they are), products of several hundred rows (the tcgen05 GEMMs with the
+    squared relu in their epilogue), prompts long enough for the memories' segments and for a window to pass inside a
+    prompt; then single tokens."""
+    from quicknn_b200.engine import Engine, Model
+    att = _att(4, 1, 128, 64, 0.09, _rot(1e5, 128))
+    raw = dict(architecture="Tumudra", vocab=1000, width=512, embedding={"scale": 2.0}, norm={"eps": 1e-5}, initializer_range=0.04,
+               layers=[_layer("parallel", {"left": _att(4, 2, 128, 128, 0.1, _rot(2e4, 64, (8.0, 1.0, 4.0, 256)), window=300),
+                                           "right": _mem(2, 64, 128, 10.0)}, 768),
+                       _layer("attention", att, 1024),
+                       _layer("retention", _ret(2, 128, 64, [0.97, 0.999], _rot(1e4, 128)), None),
+                       _layer("attention", dict(att, kv_from=1), 768)])
+    CONFIGS["L"] = (raw, 21)
+    lens, extra = [600, 130], 3
+    reqs = prompts("L", [n + extra for n in lens], seed=4)
+    for dtype in ("float32", "bfloat16"):
+        folder = make_folder(tmp_path, "L", dtype, False)
+        plain = TP.PlainTumudra(folder)
+        ref = [plain.logits(t) for t in reqs]
+        eng = Engine(Model.from_folder(folder, dtype, DEV), max_tokens=2048)
+        slots = [eng.new_sequence() for _ in reqs]
+        got = eng.step([(s, t[:n]) for s, t, n in zip(slots, reqs, lens)], "all").cpu().numpy()
+        at = 0
+        for r, n in zip(ref, lens):
+            ok, err, tol = near(got[at:at + n], r[:n], dtype)
+            assert ok, f"{dtype}: prompt of {n}: error {err:.3g} > {tol:.3g}"
+            at += n
+        for t in range(extra):
+            got = eng.step([(s, [q[n + t]]) for s, q, n in zip(slots, reqs, lens)], "last").cpu().numpy()
+            for i, (r, n) in enumerate(zip(ref, lens)):
+                ok, err, tol = near(got[i:i + 1], r[n + t:n + t + 1], dtype)
+                assert ok, f"{dtype}: request {i} decoded token {t}: error {err:.3g} > {tol:.3g}"
+
+
 # ---- configurations drawn at random ---------------------------------------------------------------------------------
 
 def random_config(seed):
