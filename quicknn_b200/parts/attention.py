@@ -217,7 +217,7 @@ class AttentionMixer(Mixer):
         here, after the attention.  Returns [rows, heads * head_dim]."""
         h = self.heads
         extend = step.mode == "extend"
-        if extend and line.writes:
+        if extend and line.writes and not self.shared_kv:
             # cached keys from before this step, this step's own rows from there on; the append comes last,
             # so that the first rows still find the ring cells that the last rows overwrite
             a = ops.attn_extend(qkv, h.n_heads, h.n_kv_heads, h.head_dim, line.k, line.v, line.page_table,

@@ -112,19 +112,19 @@ def test_a_random_folder_loads_by_its_config(tmp_path):
 
 
 def test_the_rotary_parts_frequencies_are_the_plain_ones():
-    for dims, scaling in ((8, None), (48, (8.0, 1.0, 4.0, 1024)), (6, (4.0, 1.0, 2.0, 32)), (64, (32.0, 0.5, 3.0, 16)), (0, None)):
-        rot = _rot(20000.0, dims, scaling)
-        params = {"head_dim": max(8, dims), "theta": 20000.0, "rotary_dim": dims, "layout": "interleaved"}
+    for dims, scaling in ((8, None), (56, (16.0, 1.0, 4.0, 512)), (6, (4.0, 1.0, 2.0, 32)), (64, (32.0, 0.5, 3.0, 16)), (0, None)):
+        rot = _rot(30000.0, dims, scaling)
+        params = {"head_dim": max(8, dims), "theta": 30000.0, "rotary_dim": dims, "layout": "interleaved"}
         if scaling:
             params["scaling"] = rot["scaling"]
         got = Rotary(PartSpec("rotary", params)).frequencies().numpy()
         assert got.shape == (dims // 2,) and np.allclose(got, TP.rotary_frequencies(rot), rtol=1e-12, atol=0)
-    f = TP.rotary_frequencies(_rot(20000.0, 48, (8.0, 1.0, 4.0, 1024)))
-    plain = TP.rotary_frequencies(_rot(20000.0, 48))
+    f = TP.rotary_frequencies(_rot(30000.0, 56, (16.0, 1.0, 4.0, 512)))
+    plain = TP.rotary_frequencies(_rot(30000.0, 56))
     wave = 2 * math.pi / plain
-    assert np.all(f[wave < 256] == plain[wave < 256]) and np.allclose(f[wave > 1024], plain[wave > 1024] / 8)
-    mid = (wave >= 256) & (wave <= 1024)
-    assert mid.any() and np.all(f[mid] <= plain[mid]) and np.all(f[mid] >= plain[mid] / 8)
+    assert np.all(f[wave < 128] == plain[wave < 128]) and np.allclose(f[wave > 512], plain[wave > 512] / 16)
+    mid = (wave >= 128) & (wave <= 512)
+    assert mid.any() and np.all(f[mid] <= plain[mid]) and np.all(f[mid] >= plain[mid] / 16)
 
 
 def test_the_two_rotation_layouts_are_one_rotation_under_a_permutation():
